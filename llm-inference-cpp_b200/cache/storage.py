@@ -29,6 +29,7 @@ class KVRequest:
     n_kv_heads: int
     head_dim: int
     window: int = 0          # 0: all positions
+    values: bool = True      # False: keys only (a mixer whose values are part of its key rows)
 
 
 @dataclass(frozen=True)
@@ -54,11 +55,11 @@ class KVGroup:
         self.pool = PagePool(n_pages, page_size, request.window, n_slots, max_pages_per_slot)
         shape = (n_calls, n_pages, request.n_kv_heads, page_size, request.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape, dtype=dtype, device=device) if request.values else None
 
     def bytes_per_token(self) -> int:
         r = self.request
-        return 2 * self.n_calls * r.n_kv_heads * r.head_dim * self.k.element_size()
+        return (2 if r.values else 1) * self.n_calls * r.n_kv_heads * r.head_dim * self.k.element_size()
 
 
 class StateGroup:

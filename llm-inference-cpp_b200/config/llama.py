@@ -89,6 +89,9 @@ def read_config_json(text: str) -> dict:
 
 
 def architecture_name(root: Mapping[str, Any]) -> str:
+    """The design a config.json names: ``"architectures": [name]`` (exactly one), or a single ``"architecture": name``."""
+    if "architectures" not in root and isinstance(root.get("architecture"), str):
+        return root["architecture"]
     archs = root.get("architectures")
     if not isinstance(archs, list) or len(archs) != 1 or not isinstance(archs[0], str):
         raise ConfigError('config: "architectures" must list exactly one architecture')

@@ -20,7 +20,12 @@ constexpr int OUT_ADD_F32 = 2;    // y (float) += acc       (residual sum kept i
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
 linear_simt_kernel(const T* __restrict__ x, long ldx, const T* __restrict__ w, long ldw,
-                   const float* __restrict__ bias, void* __restrict__ yv, long ldy, int M, int N, int K) {
+                   const float* __restrict__ bias, void* __restrict__ yv, long ldy, int M, int N, int K,
+                   long bx, long bw, long by) {
+  // blockIdx.z numbers the products of a batch (one per head, say): operand b starts bx, bw, by elements further on
+  x += (long)blockIdx.z * bx;
+  w += (long)blockIdx.z * bw;
+  yv = MODE == OUT_STORE ? (void*)((T*)yv + (long)blockIdx.z * by) : (void*)((float*)yv + (long)blockIdx.z * by);
   __shared__ float As[BK][BM + 4];
   __shared__ float Bs[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -95,18 +100,18 @@ linear_simt_kernel(const T* __restrict__ x, long ldx, const T* __restrict__ w, l
 
 template <typename T>
 int launch_linear_simt(const void* x, long ldx, const void* w, long ldw, const float* bias, void* y, long ldy, int M,
-                       int N, int K, int mode, cudaStream_t stream) {
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  if (grid.y > 65535) return LLMI_ERR_BAD_SIZE;
+                       int N, int K, int mode, cudaStream_t stream, int batch = 1, long bx = 0, long bw = 0, long by = 0) {
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
+  if (grid.y > 65535 || batch < 1 || batch > 65535) return LLMI_ERR_BAD_SIZE;
   switch (mode) {
     case OUT_STORE:
-      linear_simt_kernel<T, OUT_STORE><<<grid, 256, 0, stream>>>((const T*)x, ldx, (const T*)w, ldw, bias, y, ldy, M, N, K);
+      linear_simt_kernel<T, OUT_STORE><<<grid, 256, 0, stream>>>((const T*)x, ldx, (const T*)w, ldw, bias, y, ldy, M, N, K, bx, bw, by);
       break;
     case OUT_STORE_F32:
-      linear_simt_kernel<T, OUT_STORE_F32><<<grid, 256, 0, stream>>>((const T*)x, ldx, (const T*)w, ldw, bias, y, ldy, M, N, K);
+      linear_simt_kernel<T, OUT_STORE_F32><<<grid, 256, 0, stream>>>((const T*)x, ldx, (const T*)w, ldw, bias, y, ldy, M, N, K, bx, bw, by);
       break;
     case OUT_ADD_F32:
-      linear_simt_kernel<T, OUT_ADD_F32><<<grid, 256, 0, stream>>>((const T*)x, ldx, (const T*)w, ldw, bias, y, ldy, M, N, K);
+      linear_simt_kernel<T, OUT_ADD_F32><<<grid, 256, 0, stream>>>((const T*)x, ldx, (const T*)w, ldw, bias, y, ldy, M, N, K, bx, bw, by);
       break;
     default:
       return LLMI_ERR_UNSUPPORTED;
@@ -125,5 +130,19 @@ LLMI_EXPORT int llmi_linear_simt(int dtype, const void* x, long ldx, const void*
   if (dtype == LLMI_DTYPE_F32) return launch_linear_simt<float>(x, ldx, w, ldw, bias, y, ldy, M, N, K, mode, stream);
   if (dtype == LLMI_DTYPE_BF16)
     return launch_linear_simt<__nv_bfloat16>(x, ldx, w, ldw, bias, y, ldy, M, N, K, mode, stream);
+  return LLMI_ERR_BAD_DTYPE;
+}
+
+// `batch` products of the same sizes in one launch: product b reads x + b*bx, w + b*bw and writes y + b*by (offsets in
+// elements; rows may be strided, so the operands of a batch may interleave: the heads of one activation row).
+// Arithmetic and order of additions are those of llmi_linear_simt.
+LLMI_EXPORT int llmi_linear_simt_batched(int dtype, const void* x, long ldx, long bx, const void* w, long ldw, long bw,
+                                         void* y, long ldy, long by, int batch, int M, int N, int K, int mode,
+                                         cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return LLMI_ERR_BAD_SIZE;
+  if (dtype == LLMI_DTYPE_F32)
+    return launch_linear_simt<float>(x, ldx, w, ldw, nullptr, y, ldy, M, N, K, mode, stream, batch, bx, bw, by);
+  if (dtype == LLMI_DTYPE_BF16)
+    return launch_linear_simt<__nv_bfloat16>(x, ldx, w, ldw, nullptr, y, ldy, M, N, K, mode, stream, batch, bx, bw, by);
   return LLMI_ERR_BAD_DTYPE;
 }

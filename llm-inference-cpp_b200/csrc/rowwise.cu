@@ -8,10 +8,10 @@
 
 namespace llmi {
 
-// out[t, :] = float(table[ids[t], :]); a negative id (padding) gives a zero row.
+// out[t, :] = float(table[ids[t], :]) * scale; a negative id (padding) gives a zero row.
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int32_t* __restrict__ ids, float* __restrict__ out,
-                             int width) {
+                             int width, float scale) {
   pdl_launch_dependents();
   const int t = blockIdx.x;
   const int id = ids[t];
@@ -21,7 +21,11 @@ __global__ void embed_kernel(const T* __restrict__ table, const int32_t* __restr
     return;
   }
   const T* row = table + (size_t)id * width;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = to_f32(row[i]);
+  if (scale == 1.0f) {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = to_f32(row[i]);
+  } else {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = to_f32(row[i]) * scale;
+  }
 }
 
 // One block per output row.  x is the fp32 residual stream; `rows` (optional) picks the
@@ -143,8 +147,14 @@ rmsnorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ weigh
   }
 }
 
-// gate_up is [rows, 2*inner]: gate in the first half of a row, up in the second.
-template <typename T>
+// gate_up is [rows, 2*inner]: gate in the first half of a row, up in the second.  ACT 0: silu(g) = g / (1 + exp(-g));
+// ACT 1: the tanh form of GELU, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).
+template <int ACT> __device__ __forceinline__ float gate_act(float g) {
+  if (ACT == 0) return g / (1.0f + expf(-g));
+  return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+}
+
+template <typename T, int ACT>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inner, size_t total) {
   pdl_launch_dependents();
   pdl_wait();
@@ -152,8 +162,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
     const size_t r = i / inner, c = i - r * inner;
     const float g = to_f32(gate_up[r * 2 * inner + c]);
     const float u = to_f32(gate_up[r * 2 * inner + inner + c]);
-    const float s = g / (1.0f + expf(-g));
-    out[i] = from_f32<T>(s * u);
+    out[i] = from_f32<T>(gate_act<ACT>(g) * u);
   }
 }
 
@@ -162,13 +171,13 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
 using namespace llmi;
 
 LLMI_EXPORT int llmi_embed(int dtype, const void* table, const int32_t* ids, float* out, int n_tokens, int width,
-                           cudaStream_t stream) {
+                           float scale, cudaStream_t stream) {
   if (n_tokens <= 0 || width <= 0) return LLMI_ERR_BAD_SIZE;
   const int threads = width >= 1024 ? 256 : 128;
   if (dtype == LLMI_DTYPE_F32)
-    embed_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, out, width);
+    embed_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, out, width, scale);
   else if (dtype == LLMI_DTYPE_BF16)
-    embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, width);
+    embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, width, scale);
   else
     return LLMI_ERR_BAD_DTYPE;
   return launch_status();
@@ -233,17 +242,21 @@ LLMI_EXPORT int llmi_copy_to_host(void* dst, const void* src, long bytes, cudaSt
   return cudaStreamSynchronize(stream) == cudaSuccess ? LLMI_OK : LLMI_ERR_LAUNCH;
 }
 
-LLMI_EXPORT int llmi_swiglu(int dtype, const void* gate_up, void* out, int n_rows, int inner, cudaStream_t stream) {
+LLMI_EXPORT int llmi_swiglu(int dtype, const void* gate_up, void* out, int n_rows, int inner, int act, cudaStream_t stream) {
   if (n_rows <= 0 || inner <= 0) return LLMI_ERR_BAD_SIZE;
+  if (act != 0 && act != 1) return LLMI_ERR_UNSUPPORTED;
   const size_t total = (size_t)n_rows * inner;
   const int threads = 256;
   const size_t most = (size_t)sm_count() * 16;       // a grid-stride loop takes the rest
   const int blocks = (int)((total + threads - 1) / threads < most ? (total + threads - 1) / threads : most);
   if (dtype == LLMI_DTYPE_F32)
-    return launch_pdl(PDL_SMALL, swiglu_kernel<float>, blocks, threads, 0, stream, (const float*)gate_up, (float*)out, inner, total);
+    return act == 0 ? launch_pdl(PDL_SMALL, swiglu_kernel<float, 0>, blocks, threads, 0, stream, (const float*)gate_up, (float*)out, inner, total)
+                    : launch_pdl(PDL_SMALL, swiglu_kernel<float, 1>, blocks, threads, 0, stream, (const float*)gate_up, (float*)out, inner, total);
   else if (dtype == LLMI_DTYPE_BF16)
-    return launch_pdl(PDL_SMALL, swiglu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16*)gate_up,
-                      (__nv_bfloat16*)out, inner, total);
+    return act == 0 ? launch_pdl(PDL_SMALL, swiglu_kernel<__nv_bfloat16, 0>, blocks, threads, 0, stream, (const __nv_bfloat16*)gate_up,
+                                 (__nv_bfloat16*)out, inner, total)
+                    : launch_pdl(PDL_SMALL, swiglu_kernel<__nv_bfloat16, 1>, blocks, threads, 0, stream, (const __nv_bfloat16*)gate_up,
+                                 (__nv_bfloat16*)out, inner, total);
   else
     return LLMI_ERR_BAD_DTYPE;
   return launch_status();

@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from ..cache.storage import CacheBinding, KVRequest, SequenceCache, StateRequest
-from ..parts.build import build_parts, expected_tensors
+from ..parts.build import build_entries, build_parts, expected_tensors
 from ..parts.spec import ModelSpec
 from .batch import SequenceStep, StepBuffers, plan_step
 from ..ops import kernels
@@ -31,6 +31,8 @@ class Model:
         for i, call in enumerate(spec.schedule):
             if call.cache_of is not None and not (0 <= call.cache_of < len(spec.schedule)):
                 raise ValueError(f"schedule call {i} reads the cache of call {call.cache_of}, which does not exist")
+        self.entries = build_entries(spec, tensors, self.rt)      # what acts on the stream right before a call
+        self.keeps_embedding_output = any(getattr(e, "needs_embedding_output", False) for e in self.entries)
         self.buffers = StepBuffers(self.rt.device, self.rt)
         self._graphs = None
         self._prompt_graphs = None
@@ -40,6 +42,7 @@ class Model:
         parts = [self.embedding, self.final_norm, self.head]
         for layer in self.layers:
             parts += [layer.block, *layer.parts.values()]
+        parts += [e for e in self.entries if e is not None]
         self.pads_prompts = dtype == torch.bfloat16 and all(getattr(p, "takes_padding_rows", False) for p in parts)
         self.last_logits = None      # fp32 [rows, vocab] of the latest step_and_choose (scratch: valid until the next step)
         self.parameter_count = sum(int(torch.tensor(d.shape).prod()) for d in expected_tensors(spec).values())
@@ -156,13 +159,20 @@ class Model:
         x = self.embedding.forward(ctx.token_ids, ctx)
         if trace is not None:
             trace.append(x.clone())
+        x0 = None
+        if self.keeps_embedding_output:
+            x0 = self.rt.scratch("embedding_out", tuple(x.shape), torch.float32)
+            x0.copy_(x)
         # A block may hand the next one its first norm half done (norm deferral, see parts/block.py): `entry`
         # is that norm's deferred form, filled by the block before; blocks without the extras run as ever.
         blocks = [self.layers[call.layer].block for call in self.spec.schedule]
         entry = None
         for i, (block, binding) in enumerate(zip(blocks, cache.bindings)):
+            if self.entries[i] is not None:
+                self.entries[i].forward(x, x0, ctx)
+                entry = None                 # (the stream has changed since the block before looked at it)
             if hasattr(block, "entry_norm"):
-                nxt = getattr(blocks[i + 1], "entry_norm", None) if i + 1 < len(blocks) else None
+                nxt = getattr(blocks[i + 1], "entry_norm", None) if i + 1 < len(blocks) and self.entries[i + 1] is None else None
                 entry = block.forward(x, ctx, binding, entry=entry, next_norm=nxt)
             else:
                 block.forward(x, ctx, binding)

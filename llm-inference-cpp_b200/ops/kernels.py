@@ -150,9 +150,13 @@ def lib():
                      "llmi_attention_decode_mma_resident", "llmi_attention_decode_clusters_resident",
                      "llmi_attention_prefill", "llmi_attention_prefill_supported", "llmi_gemm_skinny",
                      "llmi_gemm_skinny_max_tokens", "llmi_attention_prefill_tc", "llmi_attention_prefill_tc_supported",
-                     "llmi_sm_count"):
+                     "llmi_sm_count", "llmi_dyt", "llmi_dyt_add", "llmi_stream_add", "llmi_linear_simt_batched",
+                     "llmi_latent_prepare", "llmi_latent_q_rotate", "llmi_attention_latent", "llmi_delta_prepare",
+                     "llmi_delta_conv_carry", "llmi_delta_recurrence", "llmi_delta_finish", "llmi_moe_route", "llmi_moe_up",
+                     "llmi_moe_down"):
             getattr(l, name).restype = c_int
         l.llmi_gemm_tc_workspace.restype = c_long
+        l.llmi_delta_state_floats.restype = c_long
         l.llmi_attention_decode_workspace.restype = c_long
         # The launchers of a prompt's step are called a few hundred times per step from Python: with their argument
         # types declared, plain integers go in without a ctypes object being made for each (a third of a call's cost).
@@ -167,13 +171,13 @@ def lib():
 
 # ---------------------------------------------------------------------------------------------
 
-def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t] = fp32(table[ids[t]]); ids int32 [T]; out fp32 [T, W]; a negative id gives zeros."""
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t] = fp32(table[ids[t]]) * scale; ids int32 [T]; out fp32 [T, W]; a negative id gives zeros."""
     _need_cuda(table, ids, out)
     assert ids.dtype == torch.int32 and out.dtype == torch.float32 and table.is_contiguous() and out.is_contiguous()
     T, W = out.shape
     _check("embed", lib().llmi_embed(c_int(_dtype_code(table)), _ptr(table), _ptr(ids), _ptr(out), c_int(T),
-                                     c_int(W), _stream()))
+                                     c_int(W), c_float(scale), _stream()))
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float, rows: torch.Tensor | None = None) -> None:
@@ -186,12 +190,17 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float
                                          eps, _stream_int()))
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out = silu(gate_up[:, :F]) * gate_up[:, F:]."""
+ACT_SILU, ACT_GELU_TANH = 0, 1
+ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH}
+FUSED_GATE_MODES = {ACT_SILU: OUT_SWIGLU}     # activation -> the output mode of the products that gate in their epilogue
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, act: int = ACT_SILU) -> None:
+    """out = act(gate_up[:, :F]) * gate_up[:, F:]; act: silu or the tanh form of GELU."""
     _need_cuda(gate_up, out)
     n, F = out.shape
     assert gate_up.shape == (n, 2 * F) and gate_up.is_contiguous() and out.is_contiguous() and gate_up.dtype == out.dtype
-    _check("swiglu", lib().llmi_swiglu(c_int(_dtype_code(out)), _ptr(gate_up), _ptr(out), c_int(n), c_int(F), _stream()))
+    _check("swiglu", lib().llmi_swiglu(c_int(_dtype_code(out)), _ptr(gate_up), _ptr(out), c_int(n), c_int(F), c_int(act), _stream()))
 
 
 def linear_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None,
@@ -810,3 +819,179 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, seq_p
         return
     attention_generic(qkv, out, k_cache, v_cache, ctx.tok_seq, ctx.tok_pos, seq_pages, page_size, n_heads,
                       n_kv_heads, head_dim, scale, window)
+
+
+# ---------------------------------------------------------------------------------------------
+# Dynamic Tanh, and what a looped span adds to the stream
+
+def dyt(x: torch.Tensor, weight, bias, alpha: float, out: torch.Tensor, rows: torch.Tensor | None = None) -> None:
+    """out[r] = tanh(alpha * x[src]) * weight + bias, src = rows[r] if rows is given else r; x fp32."""
+    _need_cuda(x, weight, bias, out, rows)
+    assert x.dtype == torch.float32 and weight.dtype == torch.float32 and bias.dtype == torch.float32
+    assert x.is_contiguous() and out.is_contiguous()
+    n, W = out.shape
+    assert x.shape[1] == W and weight.numel() == W and bias.numel() == W
+    _check("dyt", lib().llmi_dyt(c_int(_dtype_code(out)), _ptr(x), _ptr(weight), _ptr(bias), c_float(alpha), _ptr(out),
+                                 _ptr(rows), c_int(n), c_int(W), _stream()))
+
+
+def dyt_add(y: torch.Tensor, weight, bias, alpha: float, x: torch.Tensor, nxt=None, h: torch.Tensor | None = None) -> None:
+    """x += tanh(alpha * y) * weight + bias (y, x fp32 [T, W]); with ``nxt = (weight, bias, alpha)`` and ``h`` also
+    h = tanh(alpha' * x) * weight' + bias' of the updated x, in h's type."""
+    _need_cuda(y, weight, bias, x, h)
+    assert y.dtype == torch.float32 and x.dtype == torch.float32 and y.shape == x.shape and y.is_contiguous() and x.is_contiguous()
+    T, W = x.shape
+    w2, b2, a2 = nxt if nxt is not None else (None, None, 0.0)
+    assert (h is None) == (nxt is None)
+    if h is not None:
+        assert h.shape == x.shape and h.is_contiguous() and w2.dtype == torch.float32 and b2.dtype == torch.float32
+    _check("dyt_add", lib().llmi_dyt_add(_ptr(y), _ptr(weight), _ptr(bias), c_float(alpha), _ptr(x),
+                                         c_int(_dtype_code(h) if h is not None else 0), _ptr(h), _ptr(w2), _ptr(b2), c_float(a2),
+                                         c_int(T), c_int(W), _stream()))
+
+
+def stream_add(x: torch.Tensor, add: torch.Tensor | None, vec: torch.Tensor | None) -> None:
+    """x += add (same shape, optional), then x += vec (one row for all, optional); fp32."""
+    _need_cuda(x, add, vec)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    T, W = x.shape
+    if add is not None:
+        assert add.dtype == torch.float32 and add.shape == x.shape and add.is_contiguous()
+    if vec is not None:
+        assert vec.dtype == torch.float32 and vec.numel() == W and vec.is_contiguous()
+    _check("stream_add", lib().llmi_stream_add(_ptr(x), _ptr(add), _ptr(vec), c_int(T), c_int(W), _stream()))
+
+
+def linear_batched(x: torch.Tensor, bx: int, w: torch.Tensor, out: torch.Tensor, by: int, K: int, mode: int = OUT_STORE) -> None:
+    """``w.shape[0]`` products in one launch (one per head): out_b (mode) x_b . w[b]^T with x_b = x[:, b*bx : b*bx + K] and
+    out_b = out[:, b*by : b*by + N]; w [batch, N, K] contiguous.  fp32 FMA arithmetic in both types."""
+    _need_cuda(x, w, out)
+    B, N, Kw = w.shape
+    M = x.shape[0]
+    assert Kw == K and w.is_contiguous() and x.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == M and x.dtype == w.dtype
+    assert (B - 1) * bx + K <= x.shape[1] and (B - 1) * by + N <= out.shape[1]
+    assert out.dtype == (x.dtype if mode == OUT_STORE else torch.float32)
+    _check("linear_batched", lib().llmi_linear_simt_batched(
+        c_int(_dtype_code(x)), _ptr(x), c_long(x.stride(0)), c_long(bx), _ptr(w), c_long(K), c_long(N * K), _ptr(out),
+        c_long(out.stride(0)), c_long(by), c_int(B), c_int(M), c_int(N), c_int(K), c_int(mode), _stream()))
+
+
+# ---------------------------------------------------------------------------------------------
+# Latent attention
+
+def latent_prepare(down: torch.Tensor, Q: int, C: int, R: int, wq, wc, eps: float, inv_freq, rot_dims: int, ctx, seq_pages,
+                   page_size: int, cache: torch.Tensor, cq: torch.Tensor, write_kv: bool = True) -> None:
+    """From the fp32 down-projection rows [query latent Q | latent C | shared key part R]: the RMS-normed query
+    latent into ``cq`` (compute type) and the cache row [normed latent | rotated key part] of every token."""
+    _need_cuda(down, wq, wc, inv_freq, seq_pages, cache, cq)
+    T = down.shape[0]
+    assert down.dtype == torch.float32 and down.stride(1) == 1 and down.shape[1] >= Q + C + R
+    assert cq.shape == (T, Q) and cq.is_contiguous() and cq.dtype == cache.dtype and cache.is_contiguous()
+    assert cache.shape[-1] == C + R and cache.shape[-3] == 1 and wq.dtype == torch.float32 and wc.dtype == torch.float32
+    _check("latent_prepare", lib().llmi_latent_prepare(
+        c_int(_dtype_code(cq)), _ptr(down), c_long(down.stride(0)), c_int(Q), c_int(C), c_int(R), _ptr(wq), _ptr(wc), c_float(eps),
+        _ptr(inv_freq), c_int(rot_dims), _ptr(ctx.tok_seq), _ptr(ctx.tok_pos), _ptr(seq_pages), c_int(seq_pages.stride(0)),
+        c_int(page_size), _ptr(cache), _ptr(cq), c_int(T), c_int(1 if write_kv else 0), _stream()))
+
+
+def latent_q_rotate(q: torch.Tensor, D: int, qa: torch.Tensor, C: int, R: int, H: int, inv_freq, rot_dims: int, ctx) -> None:
+    """The part of every head's query that is rotated by position, q[:, h, D:], into qa[:, h, C:]."""
+    _need_cuda(q, qa, inv_freq)
+    T = q.shape[0]
+    assert q.dtype == qa.dtype and q.stride(1) == 1 and qa.stride(1) == 1
+    assert q.shape[1] == H * (D + R) and qa.shape == (T, H * (C + R))
+    _check("latent_q_rotate", lib().llmi_latent_q_rotate(
+        c_int(_dtype_code(q)), _ptr(q), c_long(q.stride(0)), c_int(D), _ptr(qa), c_long(qa.stride(0)), c_int(C), c_int(R), c_int(H),
+        _ptr(inv_freq), c_int(rot_dims), _ptr(ctx.tok_seq), _ptr(ctx.tok_pos), c_int(T), _stream()))
+
+
+def attention_latent(qa: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, ctx, seq_pages, page_size: int, H: int, C: int,
+                     R: int, scale: float) -> None:
+    """Causal attention of every token's heads over its sequence's latent rows: scores from all C + R entries of a
+    row, context from its first C.  qa [T, H*(C+R)], out [T, H*C]."""
+    _need_cuda(qa, out, cache, seq_pages)
+    T = qa.shape[0]
+    assert qa.dtype == out.dtype == cache.dtype and qa.stride(1) == 1 and out.stride(1) == 1 and cache.is_contiguous()
+    assert qa.shape[1] == H * (C + R) and out.shape == (T, H * C) and cache.shape[-1] == C + R and cache.shape[-3] == 1
+    _check("attention_latent", lib().llmi_attention_latent(
+        c_int(_dtype_code(qa)), _ptr(qa), c_long(qa.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(cache), _ptr(ctx.tok_seq),
+        _ptr(ctx.tok_pos), _ptr(seq_pages), c_int(seq_pages.stride(0)), c_int(page_size), c_int(T), c_int(H), c_int(C), c_int(R),
+        c_float(scale), _stream()))
+
+
+# ---------------------------------------------------------------------------------------------
+# Gated delta rule
+
+def delta_state_floats(H: int, Hk: int, D: int, Dv: int, taps: int) -> int:
+    """fp32 entries of one sequence's state: S [H, D, Dv] and the convolution's last taps-1 inputs."""
+    return int(lib().llmi_delta_state_floats(c_int(H), c_int(Hk), c_int(D), c_int(Dv), c_int(taps)))
+
+
+def delta_step(proj: torch.Tensor, dims, conv_w, a_log, dt_bias, state: torch.Tensor, ctx, prep: torch.Tensor,
+               o_raw: torch.Tensor, write_state: bool = True) -> None:
+    """The recurrent part of a gated-delta-rule mixer for one step.  ``proj`` fp32 [T, .]: [q | k | v | b | a | gate]
+    rows; ``dims = (H, Hk, D, Dv, taps)``; ``state`` [slots, state_floats] fp32 (read, and updated if
+    ``write_state``); ``prep`` fp32 [T, 2*Hk*D + H*Dv + 2*H] scratch; ``o_raw`` fp32 [T, H*Dv] receives S^T q."""
+    _need_cuda(proj, conv_w, a_log, dt_bias, state, prep, o_raw)
+    H, Hk, D, Dv, taps = dims
+    T = proj.shape[0]
+    n_conv = 2 * Hk * D + H * Dv
+    assert proj.dtype == prep.dtype == o_raw.dtype == state.dtype == torch.float32 and proj.stride(1) == 1
+    assert proj.shape[1] == n_conv + 2 * H + H * Dv and prep.shape == (T, n_conv + 2 * H) and o_raw.shape == (T, H * Dv)
+    assert prep.is_contiguous() and o_raw.is_contiguous() and state.is_contiguous() and conv_w.shape == (n_conv, taps)
+    assert conv_w.dtype == torch.float32 and conv_w.is_contiguous() and a_log.numel() == H and dt_bias.numel() == H
+    assert state.shape[-1] == delta_state_floats(H, Hk, D, Dv, taps)
+    l = lib()
+    d = (c_int(H), c_int(Hk), c_int(D), c_int(Dv), c_int(taps))
+    _check("delta_prepare", l.llmi_delta_prepare(_ptr(proj), c_long(proj.stride(0)), *d, _ptr(conv_w), _ptr(a_log), _ptr(dt_bias),
+                                                 _ptr(state), _ptr(ctx.tok_seq), _ptr(ctx.tok_pos), _ptr(ctx.seq_q_start),
+                                                 _ptr(ctx.seq_slot), _ptr(prep), c_long(prep.stride(0)), c_int(T), _stream()))
+    if write_state and taps > 1:
+        _check("delta_conv_carry", l.llmi_delta_conv_carry(_ptr(proj), c_long(proj.stride(0)), *d, _ptr(state), _ptr(ctx.seq_q_start),
+                                                           _ptr(ctx.seq_kv_len), _ptr(ctx.seq_slot), c_int(ctx.n_seqs), _stream()))
+    _check("delta_recurrence", l.llmi_delta_recurrence(_ptr(prep), c_long(prep.stride(0)), *d, _ptr(state), _ptr(ctx.seq_q_start),
+                                                       _ptr(ctx.seq_slot), _ptr(o_raw), c_long(o_raw.stride(0)), c_int(ctx.n_seqs),
+                                                       c_int(1 if write_state else 0), _stream()))
+
+
+def delta_finish(o_raw: torch.Tensor, gate: torch.Tensor, weight, eps: float, H: int, Dv: int, ctx, out: torch.Tensor) -> None:
+    """out = o / rms(o) * weight * silu(gate) per (token, head); o_raw fp32 [T, H*Dv], gate fp32 [T, H*Dv] (a strided
+    view), out in the compute type."""
+    _need_cuda(o_raw, gate, weight, out)
+    T = o_raw.shape[0]
+    assert o_raw.dtype == gate.dtype == weight.dtype == torch.float32 and gate.stride(1) == 1 and out.stride(1) == 1
+    assert gate.shape == (T, H * Dv) and out.shape == (T, H * Dv) and weight.numel() == Dv
+    _check("delta_finish", lib().llmi_delta_finish(c_int(_dtype_code(out)), _ptr(o_raw), c_long(o_raw.stride(0)), _ptr(gate),
+                                                   c_long(gate.stride(0)), _ptr(weight), c_float(eps), c_int(H), c_int(Dv),
+                                                   _ptr(ctx.tok_seq), _ptr(out), c_long(out.stride(0)), c_int(T), _stream()))
+
+
+# ---------------------------------------------------------------------------------------------
+# Routed experts
+
+def moe_route(logits: torch.Tensor, top: int, ctx, idx: torch.Tensor, wt: torch.Tensor) -> None:
+    """The ``top`` largest of each row's fp32 logits (ties: the lower index) into ``idx`` int32 [T, top], and the
+    softmax over them into ``wt`` fp32 [T, top]; a token row of no sequence gets index -1."""
+    _need_cuda(logits, idx, wt)
+    T, E = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and idx.dtype == torch.int32 and wt.dtype == torch.float32
+    assert idx.shape == (T, top) and wt.shape == (T, top) and idx.is_contiguous() and wt.is_contiguous()
+    _check("moe_route", lib().llmi_moe_route(_ptr(logits), c_long(logits.stride(0)), c_int(E), c_int(top), _ptr(ctx.tok_seq),
+                                             _ptr(idx), _ptr(wt), c_int(T), _stream()))
+
+
+def moe_experts_streamed(h: torch.Tensor, w_gate, w_up, w_down, idx, wt, act: int, a: torch.Tensor, y: torch.Tensor) -> None:
+    """y = sum over each token's choices of wt * down_e(act(gate_e h) * up_e h); the weight-streaming form.
+    w_gate, w_up [E, F, W], w_down [E, W, F] in h's type; a fp32 [T, top, F] scratch; y fp32 [T, W] (stored)."""
+    _need_cuda(h, w_gate, w_up, w_down, idx, wt, a, y)
+    T, W = h.shape
+    E, F, _ = w_gate.shape
+    top = idx.shape[1]
+    assert h.stride(1) == 1 and h.dtype == w_gate.dtype == w_up.dtype == w_down.dtype
+    assert w_gate.is_contiguous() and w_up.is_contiguous() and w_down.is_contiguous() and w_down.shape == (E, W, F)
+    assert a.dtype == torch.float32 and a.is_contiguous() and a.numel() >= T * top * F and y.dtype == torch.float32 and y.stride(1) == 1
+    l = lib()
+    _check("moe_up", l.llmi_moe_up(c_int(_dtype_code(h)), _ptr(h), c_long(h.stride(0)), _ptr(w_gate), _ptr(w_up), c_int(W), c_int(F),
+                                   c_int(top), _ptr(idx), _ptr(a), c_int(act), c_int(T), _stream()))
+    _check("moe_down", l.llmi_moe_down(c_int(_dtype_code(h)), _ptr(a), _ptr(w_down), c_int(W), c_int(F), c_int(top), _ptr(idx),
+                                       _ptr(wt), _ptr(y), c_long(y.stride(0)), c_int(T), _stream()))

@@ -9,6 +9,9 @@ the norm the plain way, so parts without these extras work unchanged.
 """
 from __future__ import annotations
 
+import torch
+
+from ..ops import kernels
 from .registry import part
 
 
@@ -32,7 +35,7 @@ class PreNormBlock:
         """``entry``: the filled deferred form of this block's first norm, or None.  ``next_norm``: the norm
         that reads x after this block, or None.  Returns that norm's deferred form if the block filled it."""
         T = x.shape[0]
-        h = entry if entry is not None else self.mixer_norm.forward(x)
+        h = entry if isinstance(entry, kernels.DeferredNorm) else self.mixer_norm.forward(x)
         then = None
         if _defers(self.mixer) and _defers(self.ffn) and hasattr(self.ffn_norm, "deferred"):
             then = self.ffn_norm.deferred(T, "deferred_inner")
@@ -42,8 +45,62 @@ class PreNormBlock:
             if then is None:
                 self.mixer.forward(h, x, ctx, binding)
             h = self.ffn_norm.forward(x)
-        then = next_norm.deferred(T, "deferred_outer") if (next_norm is not None and _defers(self.ffn)) else None
+        then = next_norm.deferred(T, "deferred_outer") if (hasattr(next_norm, "deferred") and _defers(self.ffn)) else None
         if then is not None:
             return then if self.ffn.forward(h, x, ctx, then_norm=then) else None
         self.ffn.forward(h, x, ctx)
         return None
+
+
+@part("block", "prepost")
+class PrePostNormBlock:
+    """A norm ahead of AND behind each sublayer:  x += post1(mixer(pre1(x)));  x += post2(ffn(pre2(x))).
+    Slots: ``mixer_norm``, ``mixer``, ``mixer_post`` and, for a layer with a feed-forward, ``ffn_norm``, ``ffn``,
+    ``ffn_post``.  The sublayer's output goes to an fp32 buffer of its own (a part that sets ``stores_output``
+    takes ``store=True`` and overwrites it; any other part adds into the zeroed buffer), and the norm behind it
+    joins it to the stream.  Where that norm offers ``add_to(y, x, then=)``, the norm ahead of the NEXT sublayer —
+    this block's ``ffn_norm`` or the next block's first norm — is computed in the same pass (the next block gets it
+    as ``entry``)."""
+
+    def __init__(self, mixer_norm, mixer, mixer_post, ffn_norm=None, ffn=None, ffn_post=None):
+        if (ffn is None) != (ffn_norm is None) or (ffn is None) != (ffn_post is None):
+            raise ValueError("prepost: a feed-forward comes with both of its norms, or not at all")
+        self.mixer_norm, self.mixer, self.mixer_post = mixer_norm, mixer, mixer_post
+        self.ffn_norm, self.ffn, self.ffn_post = ffn_norm, ffn, ffn_post
+        self.rt = mixer_norm.rt
+
+    @property
+    def takes_padding_rows(self) -> bool:
+        return True
+
+    @property
+    def entry_norm(self):
+        return self.mixer_norm
+
+    def _branch(self, part, h, x, *args):
+        y = self.rt.scratch("branch_out", tuple(x.shape), x.dtype)
+        if getattr(part, "stores_output", False):
+            part.forward(h, y, *args, store=True)
+        else:
+            y.zero_()
+            part.forward(h, y, *args)
+        return y
+
+    @staticmethod
+    def _join(post, y, x, then, name):
+        """x += post(y); returns then(x) if the two norms could share a pass."""
+        if hasattr(post, "add_to"):
+            return post.add_to(y, x, then if type(then) is type(post) else None, scratch_name=name)
+        x += post.forward(y, scratch_name="post_out").float()
+        return None
+
+    def forward(self, x, ctx, binding, entry=None, next_norm=None):
+        h = entry if isinstance(entry, torch.Tensor) else self.mixer_norm.forward(x)
+        y = self._branch(self.mixer, h, x, ctx, binding)
+        if self.ffn is None:
+            return self._join(self.mixer_post, y, x, next_norm, "norm_out_b")
+        h = self._join(self.mixer_post, y, x, self.ffn_norm, "norm_out_b")
+        if h is None:
+            h = self.ffn_norm.forward(x)
+        y = self._branch(self.ffn, h, x, ctx)
+        return self._join(self.ffn_post, y, x, next_norm, "norm_out")

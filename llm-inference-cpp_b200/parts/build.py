@@ -7,7 +7,7 @@ the parts appear.
 """
 from __future__ import annotations
 
-from . import attention, block, embedding, feedforward, norm, position  # noqa: F401  (register the built-in parts)
+from . import attention, block, delta, embedding, experts, feedforward, latent, loop, norm, position  # noqa: F401  (register the built-in parts)
 from .registry import TensorDecl, get_part
 from .spec import ModelSpec, PartSpec
 
@@ -17,6 +17,9 @@ def _part_specs(spec: ModelSpec):
     for layer in spec.layers:
         for _, family, ps in layer.slots():
             yield family, ps
+    for call in spec.schedule:
+        if call.before is not None:
+            yield "pass_entry", call.before
     yield "norm", spec.final_norm
     yield "head", spec.head
 
@@ -27,7 +30,7 @@ def expected_tensors(spec: ModelSpec) -> dict:
     for family, ps in _part_specs(spec):
         for local, decl in get_part(family, ps.kind).declare(ps).items():
             name = ps.prefix + local
-            if name in out and out[name].shape != decl.shape:
+            if name in out and tuple(out[name].shape) != tuple(decl.shape):
                 raise ValueError(f"tensor {name} is declared twice with different shapes")
             out[name] = decl
     return out
@@ -68,3 +71,8 @@ def build_parts(spec: ModelSpec, tensors: dict, rt):
     final_norm = _make("norm", spec.final_norm, tensors, rt)
     head = _make("head", spec.head, tensors, rt, embedding=emb)
     return emb, layers, final_norm, head
+
+
+def build_entries(spec: ModelSpec, tensors: dict, rt) -> list:
+    """The ``pass_entry`` part of every scheduled call (None where a call has none), in schedule order."""
+    return [None if call.before is None else _make("pass_entry", call.before, tensors, rt) for call in spec.schedule]

@@ -14,13 +14,15 @@ from .registry import TensorDecl, nested_build, nested_declare, part
 
 @part("embedding", "token_table")
 class TokenTable:
-    """params: ``vocab``, ``width``, optional ``position`` (a PartSpec of the position family whose
-    ``at_embedding`` acts on the looked-up rows).  tensors: ``weight [vocab, width]`` and the position part's."""
+    """params: ``vocab``, ``width``, optional ``scale`` (the looked-up rows are multiplied by it; default 1),
+    optional ``tensor`` (the table's local name; default ``weight``), optional ``position`` (a PartSpec of the
+    position family whose ``at_embedding`` acts on the looked-up rows).  tensors: the table [vocab, width] and the
+    position part's."""
     takes_padding_rows = True       # token rows of no sequence (a step padded to a shape) do no harm: rows are treated alone
 
     @classmethod
     def declare(cls, spec):
-        d = {"weight": TensorDecl((spec.params["vocab"], spec.params["width"]), "table")}
+        d = {spec.params.get("tensor", "weight"): TensorDecl((spec.params["vocab"], spec.params["width"]), "table")}
         if spec.params.get("position") is not None:
             d.update(nested_declare("position", spec.params["position"]))
         return d
@@ -28,7 +30,8 @@ class TokenTable:
     def __init__(self, spec, tensors, rt, **_):
         self.rt = rt
         self.vocab, self.width = int(spec.params["vocab"]), int(spec.params["width"])
-        self.weight = rt.to_compute(tensors["weight"])
+        self.weight = rt.to_compute(tensors[spec.params.get("tensor", "weight")])
+        self.scale = float(spec.params.get("scale", 1.0))
         pos = spec.params.get("position")
         self.position = nested_build("position", pos, tensors, rt) if pos is not None else None
 
@@ -40,7 +43,7 @@ class TokenTable:
 
     def forward(self, token_ids, ctx):
         x = self.rt.scratch("residual", (token_ids.shape[0], self.width), torch.float32)
-        kernels.embed(self.weight, token_ids, x)
+        kernels.embed(self.weight, token_ids, x, self.scale)
         if self.position is not None:
             self.position.at_embedding(x, ctx)
         return x
@@ -48,14 +51,15 @@ class TokenTable:
 
 @part("head", "linear_head")
 class LinearHead:
-    """params: ``vocab``, ``width``, ``tied``.  tensors: ``weight [vocab, width]`` unless tied."""
+    """params: ``vocab``, ``width``, ``tied``, optional ``tensor`` (the matrix's local name; default ``weight``).
+    tensors: the matrix [vocab, width] unless tied."""
     takes_padding_rows = True       # token rows of no sequence (a step padded to a shape) do no harm: rows are treated alone
 
     @classmethod
     def declare(cls, spec):
         if spec.params.get("tied", False):
             return {}
-        return {"weight": TensorDecl((spec.params["vocab"], spec.params["width"]))}
+        return {spec.params.get("tensor", "weight"): TensorDecl((spec.params["vocab"], spec.params["width"]))}
 
     def __init__(self, spec, tensors, rt, embedding=None, **_):
         self.rt = rt
@@ -66,7 +70,7 @@ class LinearHead:
                 raise ValueError("linear_head: a tied head needs the embedding part")
             self.weight = embedding.table()
         else:
-            self.weight = rt.to_compute(tensors["weight"])
+            self.weight = rt.to_compute(tensors[spec.params.get("tensor", "weight")])
 
     def weight_bytes(self) -> int:
         return 0 if self.tied else self.weight.numel() * self.weight.element_size()

@@ -40,3 +40,41 @@ class RMSNorm:
         h = self.rt.scratch(name + "_h", (n_tokens, self.width))
         ss = self.rt.scratch(name + "_ss", ((self.width + 15) // 16, kernels.DeferredNorm.SS_STRIDE), torch.float32)
         return kernels.DeferredNorm(self.weight, self.eps, h, ss)
+
+
+@part("norm", "dyt")
+class DynamicTanh:
+    """Dynamic Tanh: y = tanh(alpha * x) * weight + bias — a norm without statistics.  params: ``width``.
+    tensors (the prefix is the norm's full name): ``""`` weight [width], ``".b"`` bias [width], ``".alpha"`` a scalar;
+    all kept in fp32.  Used ahead of a sublayer (:meth:`forward`) and behind one (:meth:`add_to`: the normed
+    sublayer output joins the residual stream, and the norm ahead of the next sublayer can ride along)."""
+    takes_padding_rows = True       # elementwise: rows are treated alone
+
+    @classmethod
+    def declare(cls, spec):
+        w = spec.params["width"]
+        return {"": TensorDecl((w,), "norm_scale"), ".b": TensorDecl((w,), "bias"), ".alpha": TensorDecl((), "norm_scale")}
+
+    def __init__(self, spec, tensors, rt, **_):
+        self.width = int(spec.params["width"])
+        self.weight = rt.to_f32(tensors[""])
+        self.bias = rt.to_f32(tensors[".b"])
+        self.alpha = float(tensors[".alpha"].float().item())
+        self.rt = rt
+
+    def forward(self, x, rows=None, scratch_name: str = "norm_out"):
+        """x fp32 [tokens, width] -> rows in the compute type; ``rows`` picks input rows."""
+        n = x.shape[0] if rows is None else rows.shape[0]
+        out = self.rt.scratch(scratch_name, (n, self.width))
+        kernels.dyt(x, self.weight, self.bias, self.alpha, out, rows)
+        return out
+
+    def add_to(self, y, x, then=None, scratch_name: str = "norm_out"):
+        """x += self(y), y fp32 [tokens, width].  ``then``: another norm of this kind; its output for the updated x is
+        computed in the same pass and returned (None otherwise)."""
+        if isinstance(then, DynamicTanh):
+            h = self.rt.scratch(scratch_name, (x.shape[0], self.width))
+            kernels.dyt_add(y, self.weight, self.bias, self.alpha, x, (then.weight, then.bias, then.alpha), h)
+            return h
+        kernels.dyt_add(y, self.weight, self.bias, self.alpha, x)
+        return None

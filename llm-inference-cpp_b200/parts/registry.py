@@ -18,6 +18,8 @@ Families and what the engine calls on their members (``rt`` is the
                the spec adds under ``more``)
 ``embedding``  ``forward(token_ids, ctx) -> x`` and ``table()`` (for a tied head)
 ``head``       ``forward(h_rows) -> logits fp32 [rows, vocab]``
+``pass_entry`` ``forward(x, x0, ctx)``: acts on the stream right before a scheduled call (``ScheduleEntry.before``); ``x0`` is
+               the embedding output, kept for the step if the part sets ``needs_embedding_output``
 
 Every member also has ``declare(spec) -> {local tensor name: TensorDecl}`` (a
 classmethod: what it reads from the weight file under ``spec.prefix``) and is
@@ -47,7 +49,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
-FAMILIES = ("norm", "position", "mixer", "ffn", "block", "embedding", "head")
+FAMILIES = ("norm", "position", "mixer", "ffn", "block", "embedding", "head", "pass_entry")
 _PARTS: dict[str, dict[str, type]] = {f: {} for f in FAMILIES}
 
 

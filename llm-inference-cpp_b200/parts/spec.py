@@ -53,10 +53,13 @@ class ScheduleEntry:
     ``layer`` indexes ``ModelSpec.layers``; the same layer may be named twice.
     ``cache_of`` names the schedule position whose cache this call reads instead
     of keeping one of its own (None: its own).  A call that reads another call's
-    cache writes nothing into it.
+    cache writes nothing into it.  ``before`` is a part of the family ``pass_entry``
+    that acts on the stream right before this call (what a pass over a looped span
+    of layers adds ahead of its first layer).
     """
     layer: int
     cache_of: Optional[int] = None
+    before: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)
