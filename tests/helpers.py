@@ -121,7 +121,10 @@ def replay(model, steps, max_tokens, poison=True):
     if poison:      # whatever is read outside a sequence's own positions turns the logits to NaN
         for g in rp.cache.kv_groups:
             g.k.fill_(float("nan"))
-            g.v.fill_(float("nan"))
+            if g.v is not None:
+                g.v.fill_(float("nan"))
+        for g in rp.cache.state_groups:      # a slot's state must be cleared when the slot is handed out, not before
+            g.data.fill_(float("nan"))
     outs = []
     for s in steps:
         o = rp.run_step(s)
