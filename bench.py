@@ -98,7 +98,8 @@ def fill_cache(cache, model, batch, start_len):
     import torch
     for g in cache.kv_groups:
         g.k.normal_(0, 0.5)
-        g.v.normal_(0, 0.5)
+        if g.v is not None:
+            g.v.normal_(0, 0.5)
     slots = []
     for _ in range(batch):
         s = cache.alloc_slot()
@@ -235,6 +236,126 @@ def workload_run(name, dtypes):
     return 0
 
 
+# --design garodra: the Garodra design at sizes that resemble a real model's layers, beside the Llama decoder at equal
+# width, depth and feed-forward size.  Layers of the design alternate its two mixers and its two feed-forwards.
+def garodra_config(width, heads, dim, rot_dim, kv_rank, q_rank, d_heads, d_kv, ff, experts, top, expert_ff, layers, vocab, loop):
+    att = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": dim, "kv_rank": kv_rank, "q_rank": q_rank,
+           "scale": (dim + rot_dim) ** -0.5, "rot": {"base": 10000.0, "dims": rot_dim}}
+    dlt = {"heads": d_heads, "kv_heads": d_kv, "dim": dim, "vdim": dim, "conv": 4}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}}
+    kinds = [("latent_attention", att, dense), ("latent_attention", att, moe), ("delta", dlt, dense), ("delta", dlt, moe)]
+    cfg = {"architecture": "Garodra", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+           "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in (kinds[i % 4] for i in range(layers))]}
+    if loop:
+        cfg["loop"] = {"start": 0, "stop": layers, "times": loop}
+    return cfg
+
+
+DESIGN_SIZES = {
+    # name: (garodra config, llama config of equal width, layer runs and feed-forward size)
+    "2048": (garodra_config(2048, 16, 128, 64, 512, 1024, 16, 8, 8192, 8, 2, 2048, 8, 49152, 0),
+             dict(CONFIG, num_hidden_layers=8)),
+    "2048-looped": (garodra_config(2048, 16, 128, 64, 512, 1024, 16, 8, 8192, 8, 2, 2048, 4, 49152, 2),
+                    dict(CONFIG, num_hidden_layers=8)),
+    "1024": (garodra_config(1024, 8, 64, 32, 256, 384, 8, 4, 4096, 8, 2, 1024, 8, 49152, 0),
+             dict(CONFIG, num_hidden_layers=8, hidden_size=1024, num_attention_heads=16, num_key_value_heads=16,
+                  intermediate_size=4096)),
+}
+
+
+class KernelTimes:
+    """Device time per entry point of ops.kernels inside real steps (CUDA events around every call; steps run launch
+    by launch while this is on, so the figures are shares of a step, not a benchmark of it)."""
+    NAMES = ("embed", "rmsnorm", "swiglu", "linear", "rope_store", "attention", "dyt", "dyt_add", "stream_add", "linear_batched",
+             "latent_prepare", "latent_q_rotate", "attention_latent", "delta_step", "delta_finish", "moe_route",
+             "moe_experts_streamed", "moe_experts_grouped")
+
+    def __init__(self):
+        self.spans, self.saved = [], {}
+
+    def __enter__(self):
+        import torch
+        from llmi_b200.ops import kernels
+        for name in self.NAMES:
+            fn = getattr(kernels, name, None)
+            if fn is None:
+                continue
+            self.saved[name] = fn
+
+            def timed(*a, _fn=fn, _name=name, **k):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                r = _fn(*a, **k)
+                e1.record()
+                self.spans.append((_name, e0, e1))
+                return r
+            setattr(kernels, name, timed)
+        return self
+
+    def __exit__(self, *exc):
+        from llmi_b200.ops import kernels
+        for name, fn in self.saved.items():
+            setattr(kernels, name, fn)
+
+    def table(self):
+        import torch
+        torch.cuda.synchronize()
+        out = {}
+        for name, e0, e1 in self.spans:
+            out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
+        return {k: round(v, 3) for k, v in sorted(out.items(), key=lambda kv: -kv[1])}
+
+
+def design_run(name, steps, warmup, batch, context, tokens, sizes):
+    """Prefill and decode throughput of a design beside the closest existing model at equal size; one JSON line."""
+    import torch
+    import llmi_b200 as L
+    from llmi_b200 import SequenceStep
+    if name != "garodra":
+        print(f"bench.py: unknown design {name!r}")
+        return 2
+    pk, pk_kind = peaks()
+    out = {"design": name, "impl": "ours", "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids, random cache contents)",
+           "batch": batch, "context": context, "prefill_tokens": tokens, "steps": steps, "warmup": warmup, "peaks": pk_kind,
+           "sizes": {}}
+    for size in sizes:
+        g_cfg, l_cfg = DESIGN_SIZES[size]
+        row = {}
+        for label, cfg in (("garodra", g_cfg), ("llama", l_cfg)):
+            model = L.random_model(cfg, seed=0, dtype="bfloat16", on_device=True)
+            pre_ms = prefill_run(model, tokens, iters=3)
+            ms, launches, _, _, cache_bytes = decode_run(model, batch, context, steps, warmup)
+            ms1, *_ = decode_run(model, 1, context, min(steps, 32), warmup)
+            entry = {"params": model.parameter_count, "weight_bytes": model.weight_bytes(),
+                     "prefill_ms": round(pre_ms, 3), "prefill_tokens_per_s": round(tokens * 1000.0 / pre_ms, 1),
+                     "decode_ms_per_step": round(ms, 4), "decode_tokens_per_s": round(batch * 1000.0 / ms, 1),
+                     "decode_b1_tokens_per_s": round(1000.0 / ms1, 1), "decode_launches": launches,
+                     "cache_bytes_per_token": model.new_cache(64).bytes_per_token()}
+            # shares of one prompt step and of one decode step, kernel by kernel (launch by launch)
+            os.environ["LLMI_GRAPHS"] = "0"
+            from llmi_b200.engine import graphs
+            graphs.RECORD = False
+            cache = model.new_cache(((tokens + 63) // 64) * 64 + 64)
+            ids = torch.randint(0, model.vocab_size, (tokens,), generator=torch.Generator().manual_seed(1)).tolist()
+            slot = cache.alloc_slot()
+            with KernelTimes() as kt:
+                model.step(cache, [SequenceStep(slot, ids, [tokens - 1])])
+            entry["prefill_kernel_ms"] = kt.table()
+            with KernelTimes() as kt:
+                model.step(cache, [SequenceStep(slot, [1], [0])])
+            entry["decode_b1_kernel_ms_at_%d" % tokens] = kt.table()
+            cache.free_slot(slot)
+            graphs.RECORD = True
+            os.environ.pop("LLMI_GRAPHS", None)
+            row[label] = entry
+            del model, cache
+            torch.cuda.empty_cache()
+        out["sizes"][size] = row
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -253,8 +374,18 @@ def main():
     ap.add_argument("--workload-dtypes", default="bfloat16", help="comma-separated: bfloat16, float32")
     ap.add_argument("--kv-heads", type=int, default=None,
                     help="with --only: another number of key/value heads (grouped queries), to profile their kernels")
+    ap.add_argument("--design", default=None,
+                    help="'garodra': that design's prefill and decode throughput at layer sizes of a real model, beside the "
+                         "Llama decoder at equal size (its own JSON line; the default workload is untouched)")
+    ap.add_argument("--design-sizes", default="2048,1024", help="with --design: which of " + ", ".join(sorted(DESIGN_SIZES)))
     args = ap.parse_args()
 
+    if args.design:
+        if args.gpus != 1:
+            print("bench.py: this library runs on one GPU; --gpus must be 1")
+            return 2
+        return design_run(args.design, max(args.steps, 1) if args.steps != 256 else 64, max(args.warmup, 3), args.batch,
+                          args.context, args.prefill_tokens, [x.strip() for x in args.design_sizes.split(",") if x.strip()])
     if args.impl == "reference":
         if args.gpus != 1:
             print(json.dumps({"impl": "reference", "unavailable": "the reference runs on the CPU of one machine; --gpus must be 1"}))

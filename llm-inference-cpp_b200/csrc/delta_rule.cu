@@ -192,6 +192,88 @@ delta_recurrence_kernel(const float* __restrict__ prep, long ldp, DeltaDims m, f
   }
 }
 
+// The same with FOUR lanes per column of S (D = 4 * DQ, the column's entries d = sub, sub + 4, ... in registers of lane
+// `sub`): a quarter of the serial work per token and of the registers, partial sums joined by two shuffles.  The
+// recurrence is a chain over the tokens, so the time of a prompt is tokens x (time of one token): this form is what
+// keeps that time short.
+template <int DQ>
+__global__ void __launch_bounds__(512)
+delta_recurrence_quad_kernel(const float* __restrict__ prep, long ldp, DeltaDims m, float* __restrict__ state,
+                             const int32_t* __restrict__ seq_q_start, const int32_t* __restrict__ seq_slot,
+                             float* __restrict__ o_raw, long ldo, int write_state) {
+  extern __shared__ float sm[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int h = blockIdx.x, seq = blockIdx.y;
+  const int slot = seq_slot[seq];
+  if (slot < 0) return;
+  const int r0 = seq_q_start[seq], n = seq_q_start[seq + 1] - r0;
+  if (n <= 0) return;
+  constexpr int D = 4 * DQ;
+  const int Dv = m.Dv;
+  const int col = threadIdx.x >> 2, sub = threadIdx.x & 3;
+  const bool live = col < Dv;
+  const int j = live ? col : Dv - 1;
+  float* kq = sm;                                            // [2][2*D]
+  const int kh = h / (m.H / m.Hk);
+  float* S_g = state + (size_t)slot * m.state_floats() + (size_t)h * D * Dv;
+  float S_r[DQ];
+#pragma unroll
+  for (int i = 0; i < DQ; ++i) S_r[i] = S_g[(size_t)(sub + 4 * i) * Dv + j];
+  const int Nc = m.n_conv();
+  auto fetch = [&](int i, int buf) {
+    const float* row = prep + (size_t)(r0 + i) * ldp;
+    for (int d = threadIdx.x; d < 2 * D; d += blockDim.x)
+      kq[buf * 2 * D + d] = d < D ? row[(size_t)m.Hk * D + (size_t)kh * D + d] : row[(size_t)kh * D + (d - D)];
+  };
+  fetch(0, 0);
+  for (int i = 0; i < n; ++i) {
+    __syncthreads();
+    if (i + 1 < n) fetch(i + 1, (i + 1) & 1);
+    const float* row = prep + (size_t)(r0 + i) * ldp;
+    const float v = row[(size_t)m.n_qk() + (size_t)h * Dv + j];
+    const float beta = row[Nc + h], g = row[Nc + m.H + h];
+    const float* k = kq + (i & 1) * 2 * D + sub;
+    const float* q = k + D;
+    float p0 = 0.f, p1 = 0.f;
+#pragma unroll
+    for (int e = 0; e < DQ; e += 2) {
+      p0 = fmaf(S_r[e], k[4 * e], p0);
+      p1 = fmaf(S_r[e + 1], k[4 * e + 4], p1);
+    }
+    float sk = p0 + p1;
+    sk += __shfl_xor_sync(0xffffffffu, sk, 1);
+    sk += __shfl_xor_sync(0xffffffffu, sk, 2);
+    const float u = beta * (v - g * sk);
+    float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+    for (int e = 0; e < DQ; e += 2) {
+      const float s0 = fmaf(k[4 * e], u, g * S_r[e]), s1 = fmaf(k[4 * e + 4], u, g * S_r[e + 1]);
+      S_r[e] = s0;
+      S_r[e + 1] = s1;
+      o0 = fmaf(s0, q[4 * e], o0);
+      o1 = fmaf(s1, q[4 * e + 4], o1);
+    }
+    float o = o0 + o1;
+    o += __shfl_xor_sync(0xffffffffu, o, 1);
+    o += __shfl_xor_sync(0xffffffffu, o, 2);
+    if (live && sub == 0) o_raw[(size_t)(r0 + i) * ldo + (size_t)h * Dv + j] = o;
+  }
+  if (live && write_state) {
+#pragma unroll
+    for (int i = 0; i < DQ; ++i) S_g[(size_t)(sub + 4 * i) * Dv + j] = S_r[i];
+  }
+}
+
+template <int DQ>
+int launch_delta_recurrence_quad(const float* prep, long ldp, DeltaDims m, float* state, const int32_t* seq_q_start,
+                                 const int32_t* seq_slot, float* o_raw, long ldo, int n_seqs, int write_state,
+                                 cudaStream_t stream) {
+  const int threads = (4 * m.Dv + 31) / 32 * 32;
+  return launch_pdl(PDL_ATTENTION, delta_recurrence_quad_kernel<DQ>, dim3(m.H, n_seqs), dim3(threads), (size_t)16 * DQ * sizeof(float),
+                    stream, prep, ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, write_state);
+}
+
 // One warp per (token, head): out = o / sqrt(mean(o^2) + eps) * w * silu(gate).
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -273,8 +355,11 @@ LLMI_EXPORT int llmi_delta_recurrence(const float* prep, long ldp, int H, int Hk
                                       int write_state, cudaStream_t stream) {
   const DeltaDims m{H, Hk, D, Dv, taps};
   if (n_seqs <= 0 || n_seqs > 65535 || !delta_dims_ok(m)) return LLMI_ERR_BAD_SIZE;
-  if (D == 64) return launch_delta_recurrence<64>(prep, ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, n_seqs, write_state, stream);
-  if (D == 128) return launch_delta_recurrence<128>(prep, ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, n_seqs, write_state, stream);
+  if (Dv <= 128) {
+    if (D == 32) return launch_delta_recurrence_quad<8>(prep, ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, n_seqs, write_state, stream);
+    if (D == 64) return launch_delta_recurrence_quad<16>(prep, ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, n_seqs, write_state, stream);
+    if (D == 128) return launch_delta_recurrence_quad<32>(prep, ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, n_seqs, write_state, stream);
+  }
   if ((size_t)D * ((Dv + 31) / 32 * 32) * 4 + 16 * (size_t)D > 200 * 1024) return LLMI_ERR_BAD_SIZE;
   return launch_delta_recurrence<0>(prep, ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, n_seqs, write_state, stream);
 }

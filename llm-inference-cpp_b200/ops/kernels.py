@@ -153,10 +153,12 @@ def lib():
                      "llmi_sm_count", "llmi_dyt", "llmi_dyt_add", "llmi_stream_add", "llmi_linear_simt_batched",
                      "llmi_latent_prepare", "llmi_latent_q_rotate", "llmi_attention_latent", "llmi_delta_prepare",
                      "llmi_delta_conv_carry", "llmi_delta_recurrence", "llmi_delta_finish", "llmi_moe_route", "llmi_moe_up",
-                     "llmi_moe_down"):
+                     "llmi_moe_down", "llmi_moe_grouped", "llmi_attention_latent_mma", "llmi_attention_latent_mma_supported"):
             getattr(l, name).restype = c_int
         l.llmi_gemm_tc_workspace.restype = c_long
         l.llmi_delta_state_floats.restype = c_long
+        l.llmi_attention_latent_mma_workspace.restype = c_long
+        l.llmi_moe_group_ints.restype = c_long
         l.llmi_attention_decode_workspace.restype = c_long
         # The launchers of a prompt's step are called a few hundred times per step from Python: with their argument
         # types declared, plain integers go in without a ctypes object being made for each (a third of a call's cost).
@@ -905,14 +907,44 @@ def latent_q_rotate(q: torch.Tensor, D: int, qa: torch.Tensor, C: int, R: int, H
         _ptr(inv_freq), c_int(rot_dims), _ptr(ctx.tok_seq), _ptr(ctx.tok_pos), c_int(T), _stream()))
 
 
+_LATENT_ATTENTION = os.environ.get("LLMI_LATENT_ATTENTION", "mma")      # "generic": the fp32-arithmetic kernel for everything
+
+
+def latent_attention_plan(ctx, n_tokens: int, n_pages: int, H: int) -> tuple:
+    """(cuts over the positions, pages per cut) of the tensor-core latent attention for a step: prompts are not cut;
+    a step of single tokens is cut until about two blocks per SM are at work.  Depends on the step's padded shape
+    only, so a recorded step can be replayed."""
+    if not ctx.decode:
+        return 1, max(n_pages, 1)
+    hpb = 1
+    while hpb < H and hpb < 16:
+        hpb *= 2
+    blocks = -(-n_tokens // (16 // hpb)) * -(-H // hpb)
+    want = max(1, min(n_pages, -(-2 * sm_count() // blocks)))
+    pps = -(-n_pages // want)
+    return -(-n_pages // pps), pps
+
+
 def attention_latent(qa: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, ctx, seq_pages, page_size: int, H: int, C: int,
-                     R: int, scale: float) -> None:
+                     R: int, scale: float, rt=None) -> None:
     """Causal attention of every token's heads over its sequence's latent rows: scores from all C + R entries of a
-    row, context from its first C.  qa [T, H*(C+R)], out [T, H*C]."""
+    row, context from its first C.  qa [T, H*(C+R)], out [T, H*C].  bf16 sizes that the tensor-core kernel takes go
+    there (``rt`` lends the workspace of its cuts); everything else, and the 32-bit path, to the generic kernel."""
     _need_cuda(qa, out, cache, seq_pages)
     T = qa.shape[0]
     assert qa.dtype == out.dtype == cache.dtype and qa.stride(1) == 1 and out.stride(1) == 1 and cache.is_contiguous()
     assert qa.shape[1] == H * (C + R) and out.shape == (T, H * C) and cache.shape[-1] == C + R and cache.shape[-3] == 1
+    if (qa.dtype == torch.bfloat16 and rt is not None and _LATENT_ATTENTION == "mma"
+            and lib().llmi_attention_latent_mma_supported(c_int(C), c_int(R), c_int(page_size))
+            and qa.data_ptr() % 16 == 0 and qa.stride(0) % 8 == 0):
+        splits, pps = latent_attention_plan(ctx, T, seq_pages.shape[1], H)
+        n_ws = int(lib().llmi_attention_latent_mma_workspace(c_int(T), c_int(H), c_int(C), c_int(splits)))
+        ws = rt.scratch("latent_partials", (n_ws,), torch.float32) if n_ws else None
+        _check("attention_latent_mma", lib().llmi_attention_latent_mma(
+            _ptr(qa), c_long(qa.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(cache), _ptr(ctx.tok_seq), _ptr(ctx.tok_pos),
+            _ptr(seq_pages), c_int(seq_pages.stride(0)), c_int(page_size), c_int(T), c_int(H), c_int(C), c_int(R), c_float(scale),
+            c_int(splits), c_int(pps), _ptr(ws), c_long(n_ws), _stream()))
+        return
     _check("attention_latent", lib().llmi_attention_latent(
         c_int(_dtype_code(qa)), _ptr(qa), c_long(qa.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(cache), _ptr(ctx.tok_seq),
         _ptr(ctx.tok_pos), _ptr(seq_pages), c_int(seq_pages.stride(0)), c_int(page_size), c_int(T), c_int(H), c_int(C), c_int(R),
@@ -995,3 +1027,32 @@ def moe_experts_streamed(h: torch.Tensor, w_gate, w_up, w_down, idx, wt, act: in
                                    c_int(top), _ptr(idx), _ptr(a), c_int(act), c_int(T), _stream()))
     _check("moe_down", l.llmi_moe_down(c_int(_dtype_code(h)), _ptr(a), _ptr(w_down), c_int(W), c_int(F), c_int(top), _ptr(idx),
                                        _ptr(wt), _ptr(y), c_long(y.stride(0)), c_int(T), _stream()))
+
+
+MOE_GROUPED_MIN_TOKENS = int(os.environ.get("LLMI_MOE_GROUPED_MIN", "33"))
+
+
+def moe_grouped_applies(h: torch.Tensor, W: int, F: int, E: int) -> bool:
+    """Whether a step's routed experts run as grouped tensor-core tiles (bf16, many tokens) or stream their weights."""
+    return bool(h.dtype == torch.bfloat16 and h.shape[0] >= MOE_GROUPED_MIN_TOKENS and W % 8 == 0 and F % 8 == 0 and E <= 256
+                and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0 and not _FORCE_SIMT)
+
+
+def moe_experts_grouped(h: torch.Tensor, w_gate, w_up, w_down, idx, wt, act: int, rt, y: torch.Tensor) -> None:
+    """The same result as :func:`moe_experts_streamed` for many tokens: the (token, choice) items are grouped by expert
+    and each expert's products run as tensor-core tiles over its rows.  bf16; ``rt`` lends the scratch."""
+    _need_cuda(h, w_gate, w_up, w_down, idx, wt, y)
+    T, W = h.shape
+    E, F, _ = w_gate.shape
+    top = idx.shape[1]
+    assert h.dtype == w_gate.dtype == w_up.dtype == w_down.dtype == torch.bfloat16 and h.stride(1) == 1
+    assert w_gate.is_contiguous() and w_up.is_contiguous() and w_down.is_contiguous() and w_down.shape == (E, W, F)
+    assert y.dtype == torch.float32 and y.stride(1) == 1 and idx.is_contiguous() and wt.is_contiguous()
+    n_int = int(lib().llmi_moe_group_ints(c_int(T * top), c_int(E)))
+    scratch = rt.scratch("experts_groups", (n_int,), torch.int32)
+    a_sorted = rt.scratch("experts_act_sorted", (T * top, F), torch.bfloat16)
+    y_sorted = rt.scratch("experts_out_sorted", (T * top, W), torch.float32)
+    _check("moe_grouped", lib().llmi_moe_grouped(
+        _ptr(h), c_long(h.stride(0)), _ptr(w_gate), _ptr(w_up), _ptr(w_down), c_int(W), c_int(F), c_int(E), c_int(top), _ptr(idx),
+        _ptr(wt), c_int(act), _ptr(scratch), c_long(n_int), _ptr(a_sorted), _ptr(y_sorted), _ptr(y), c_long(y.stride(0)), c_int(T),
+        _stream()))

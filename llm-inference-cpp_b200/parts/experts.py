@@ -56,9 +56,12 @@ class RoutedExperts:
         idx = rt.scratch("router_choice", (T, self.top), torch.int32)
         wt = rt.scratch("router_weight", (T, self.top), torch.float32)
         kernels.moe_route(logits, self.top, ctx, idx, wt)
-        a = rt.scratch("experts_act", (T, self.top, self.inner), torch.float32)
         y = x if store else rt.scratch("experts_out", tuple(x.shape), torch.float32)
-        kernels.moe_experts_streamed(h, self.w_gate, self.w_up, self.w_down, idx, wt, self.act, a, y)
+        if kernels.moe_grouped_applies(h, self.width, self.inner, self.E):
+            kernels.moe_experts_grouped(h, self.w_gate, self.w_up, self.w_down, idx, wt, self.act, rt, y)
+        else:
+            a = rt.scratch("experts_act", (T, self.top, self.inner), torch.float32)
+            kernels.moe_experts_streamed(h, self.w_gate, self.w_up, self.w_down, idx, wt, self.act, a, y)
         if not store:
             x += y
         return False

@@ -86,7 +86,7 @@ class LatentAttention:
         kernels.linear_batched(q, D + R, self.w_uk_t, qa, C + R, D)
         kernels.latent_q_rotate(q, D, qa, C, R, H, self.inv_freq, self.rot_dims, ctx)
         lat = rt.scratch("latent_ctx", (T, H * C))
-        kernels.attention_latent(qa, lat, cache, ctx, pages, g.page_size, H, C, R, self.scale)
+        kernels.attention_latent(qa, lat, cache, ctx, pages, g.page_size, H, C, R, self.scale, rt=rt)
         heads = rt.scratch("attn_out", (T, H * Dv))
         kernels.linear_batched(lat, C, self.w_uv, heads, Dv, C)
         kernels.linear(heads, self.w_o, x, None, kernels.OUT_STORE_F32 if store else kernels.OUT_ADD_F32)

@@ -214,7 +214,8 @@ def test_latent_attention_finds_one_key_among_hundreds(far, dtype):
         pass
     dt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
     rng = np.random.default_rng(far)
-    N, H, C, R, page = 300, 3, 40, 8, 64
+    N, H, page = 300, 3, 64
+    C, R = (40, 8) if far % 2 else (64, 16)                       # odd: the generic kernel; even: sizes the tensor-core kernel takes
     rows = rng.standard_normal((N, C + R)).astype(np.float32)
     q = rng.standard_normal((H, C + R)).astype(np.float32) * 0.3
     q[1] = rows[far] * 4.0                                        # score of `far` for head 1: 4 |row|^2, about 190
@@ -225,18 +226,45 @@ def test_latent_attention_finds_one_key_among_hundreds(far, dtype):
     for i, pg in enumerate(order):
         n = min(page, N - i * page)
         cache[pg, 0, :n] = rows_t[i * page:i * page + n].to("cuda:0")
+    from llmi_b200.engine.runtime import Runtime
     ctx = Ctx()
+    ctx.decode = True
     ctx.tok_seq = torch.zeros(1, dtype=torch.int32, device="cuda:0")
     ctx.tok_pos = torch.full((1,), N - 1, dtype=torch.int32, device="cuda:0")
     pages = torch.tensor(order[None, :].astype(np.int32), device="cuda:0")
     out = torch.empty((1, H * C), dtype=dt, device="cuda:0")
-    kernels.attention_latent(q_t.reshape(1, -1).to("cuda:0"), out, cache, ctx, pages, page, H, C, R, 1.0)
+    kernels.attention_latent(q_t.reshape(1, -1).to("cuda:0"), out, cache, ctx, pages, page, H, C, R, 1.0, rt=Runtime(dt, "cuda:0"))
     rr, qq = rows_t.float().numpy().astype(np.float64), q_t.float().numpy().astype(np.float64)
     ref = G.softmax(qq @ rr.T) @ rr[:, :C]
     got = out.float().cpu().numpy().reshape(H, C)
     tol = 1e-5 if dtype == "float32" else 2e-2
     assert np.abs(got - ref).max() < tol
     assert np.abs(got[1] - rr[far, :C]).max() < tol              # head 1 sees the one row
+
+
+@pytest.mark.parametrize("T,E,top,W,F", [(40, 5, 2, 64, 40), (200, 8, 3, 128, 72), (33, 3, 3, 72, 8), (130, 70, 1, 64, 64)])
+def test_grouped_experts_equal_streamed_experts(T, E, top, W, F):
+    """The tensor-core form for many tokens against the weight-streaming form, same choices and weights: equal up to the
+    rounding of the activations to bf16; a row of no sequence gets zeros."""
+    import torch
+    from llmi_b200.engine.runtime import Runtime
+    from llmi_b200.ops import kernels
+    rt = Runtime(torch.bfloat16, "cuda:0")
+    gen = torch.Generator(device="cuda:0").manual_seed(T)
+
+    def rnd(*shape, gain=1.0):
+        return (torch.randn(*shape, generator=gen, device="cuda:0") * gain).to(torch.bfloat16)
+    h, wg, wu, wd = rnd(T, W), rnd(E, F, W, gain=W ** -0.5), rnd(E, F, W, gain=W ** -0.5), rnd(E, W, F, gain=F ** -0.5)
+    idx = torch.stack([torch.randperm(E, generator=gen, device="cuda:0")[:top] for _ in range(T)]).to(torch.int32).contiguous()
+    wt = torch.rand(T, top, generator=gen, device="cuda:0")
+    idx[7] = -1
+    a = torch.empty(T, top, F, dtype=torch.float32, device="cuda:0")
+    y_s = torch.full((T, W), float("nan"), device="cuda:0")
+    y_g = torch.full((T, W), float("nan"), device="cuda:0")
+    kernels.moe_experts_streamed(h, wg, wu, wd, idx, wt, kernels.ACT_SILU, a, y_s)
+    kernels.moe_experts_grouped(h, wg, wu, wd, idx, wt, kernels.ACT_SILU, rt, y_g)
+    assert torch.isfinite(y_g).all() and (y_g[7] == 0).all()
+    assert float((y_g - y_s).abs().max()) < 2e-2 * max(1.0, float(y_s.abs().max()))
 
 
 def test_the_oracle_itself_the_folded_form_of_latent_attention():
