@@ -214,25 +214,32 @@ delta_recurrence_quad_kernel(const float* __restrict__ prep, long ldp, DeltaDims
   const int col = threadIdx.x >> 2, sub = threadIdx.x & 3;
   const bool live = col < Dv;
   const int j = live ? col : Dv - 1;
-  float* kq = sm;                                            // [2][2*D]
+  float* kq = sm;                                            // [2][2*D]: k then q of a token
   const int kh = h / (m.H / m.Hk);
   float* S_g = state + (size_t)slot * m.state_floats() + (size_t)h * D * Dv;
   float S_r[DQ];
 #pragma unroll
   for (int i = 0; i < DQ; ++i) S_r[i] = S_g[(size_t)(sub + 4 * i) * Dv + j];
   const int Nc = m.n_conv();
-  auto fetch = [&](int i, int buf) {
-    const float* row = prep + (size_t)(r0 + i) * ldp;
-    for (int d = threadIdx.x; d < 2 * D; d += blockDim.x)
-      kq[buf * 2 * D + d] = d < D ? row[(size_t)m.Hk * D + (size_t)kh * D + d] : row[(size_t)kh * D + (d - D)];
-  };
-  fetch(0, 0);
+  // What the NEXT token needs is asked for before the current token is computed and put down after it, so that
+  // no load's latency lies on the chain from token to token: the entry of [k | q] this thread copies (the first 2*D
+  // threads; 4 * Dv >= 2 * D is checked by the launcher), and v, beta, g.
+  const bool copies = (int)threadIdx.x < 2 * D;
+  const size_t kq_off = (int)threadIdx.x < D ? (size_t)m.Hk * D + (size_t)kh * D + threadIdx.x : (size_t)kh * D + (threadIdx.x - D);
+  const size_t v_off = (size_t)m.n_qk() + (size_t)h * Dv + j;
+  const float* row = prep + (size_t)r0 * ldp;
+  if (copies) kq[threadIdx.x] = row[kq_off];
+  float v = row[v_off], beta = row[Nc + h], g = row[Nc + m.H + h];
   for (int i = 0; i < n; ++i) {
-    __syncthreads();
-    if (i + 1 < n) fetch(i + 1, (i + 1) & 1);
-    const float* row = prep + (size_t)(r0 + i) * ldp;
-    const float v = row[(size_t)m.n_qk() + (size_t)h * Dv + j];
-    const float beta = row[Nc + h], g = row[Nc + m.H + h];
+    __syncthreads();                                         // buffer i&1 is filled; the other one is read out
+    float n_kq = 0.f, n_v = 0.f, n_beta = 0.f, n_g = 0.f;
+    if (i + 1 < n) {
+      const float* nxt = prep + (size_t)(r0 + i + 1) * ldp;
+      if (copies) n_kq = nxt[kq_off];
+      n_v = nxt[v_off];
+      n_beta = nxt[Nc + h];
+      n_g = nxt[Nc + m.H + h];
+    }
     const float* k = kq + (i & 1) * 2 * D + sub;
     const float* q = k + D;
     float p0 = 0.f, p1 = 0.f;
@@ -258,6 +265,8 @@ delta_recurrence_quad_kernel(const float* __restrict__ prep, long ldp, DeltaDims
     o += __shfl_xor_sync(0xffffffffu, o, 1);
     o += __shfl_xor_sync(0xffffffffu, o, 2);
     if (live && sub == 0) o_raw[(size_t)(r0 + i) * ldo + (size_t)h * Dv + j] = o;
+    if (copies && i + 1 < n) kq[((i + 1) & 1) * 2 * D + threadIdx.x] = n_kq;
+    v = n_v; beta = n_beta; g = n_g;
   }
   if (live && write_state) {
 #pragma unroll
@@ -355,7 +364,7 @@ LLMI_EXPORT int llmi_delta_recurrence(const float* prep, long ldp, int H, int Hk
                                       int write_state, cudaStream_t stream) {
   const DeltaDims m{H, Hk, D, Dv, taps};
   if (n_seqs <= 0 || n_seqs > 65535 || !delta_dims_ok(m)) return LLMI_ERR_BAD_SIZE;
-  if (Dv <= 128) {
+  if (Dv <= 128 && 4 * ((Dv + 7) / 8 * 8) >= 2 * D) {          // (the block's threads also copy [k | q]: 2 * D entries)
     if (D == 32) return launch_delta_recurrence_quad<8>(prep, ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, n_seqs, write_state, stream);
     if (D == 64) return launch_delta_recurrence_quad<16>(prep, ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, n_seqs, write_state, stream);
     if (D == 128) return launch_delta_recurrence_quad<32>(prep, ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, n_seqs, write_state, stream);

@@ -66,11 +66,48 @@ template <int ACT> __device__ __forceinline__ float moe_act(float g) {
   return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
 }
 
-// grid (T * top, ceil(F / rows per block)); 8 warps, one output f per warp at a time.
-template <typename T, int ACT>
+// A warp's dot product of a shared-memory fp32 vector with one weight row, 16 bytes per lane and load.
+template <typename T> struct Vec16;
+template <> struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  }
+};
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+    const float4 f = *reinterpret_cast<const float4*>(p);
+    v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+  }
+};
+
+// VEC: rows are 16-byte aligned and a multiple of 16 bytes long.  The order of a row's additions is fixed by (K, VEC).
+template <typename T, bool VEC>
+__device__ __forceinline__ float warp_dot(const float* __restrict__ x_s, const T* __restrict__ row, int K, int lane) {
+  float acc = 0.f;
+  if (VEC) {
+    constexpr int N = Vec16<T>::N;
+    for (int i = lane * N; i < K; i += 32 * N) {
+      float v[N];
+      Vec16<T>::load(row + i, v);
+#pragma unroll
+      for (int e = 0; e < N; ++e) acc = fmaf(x_s[i + e], v[e], acc);
+    }
+  } else {
+    for (int i = lane; i < K; i += 32) acc = fmaf(x_s[i], to_f32(row[i]), acc);
+  }
+  return warp_sum(acc);
+}
+
+// grid (T * top, ceil(F / 8)); 8 warps, one output f per warp.
+template <typename T, int ACT, bool VEC>
 __global__ void __launch_bounds__(256)
 moe_up_kernel(const T* __restrict__ h, long ldh, const T* __restrict__ wg, const T* __restrict__ wu, int W, int F, int top,
-              const int32_t* __restrict__ idx, float* __restrict__ a, int f_per_block) {
+              const int32_t* __restrict__ idx, float* __restrict__ a) {
   extern __shared__ float h_s[];
   pdl_launch_dependents();
   pdl_wait();
@@ -80,45 +117,35 @@ moe_up_kernel(const T* __restrict__ h, long ldh, const T* __restrict__ wg, const
   for (int i = threadIdx.x; i < W; i += blockDim.x) h_s[i] = to_f32(h[(size_t)t * ldh + i]);
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int f0 = blockIdx.y * f_per_block, f1 = min(F, f0 + f_per_block);
-  for (int f = f0 + warp; f < f1; f += 8) {
-    const T* g_row = wg + ((size_t)e * F + f) * W;
-    const T* u_row = wu + ((size_t)e * F + f) * W;
-    float g = 0.f, u = 0.f;
-    for (int i = lane; i < W; i += 32) {
-      g = fmaf(h_s[i], to_f32(g_row[i]), g);
-      u = fmaf(h_s[i], to_f32(u_row[i]), u);
-    }
-    g = warp_sum(g);
-    u = warp_sum(u);
-    if (lane == 0) a[(size_t)item * F + f] = moe_act<ACT>(g) * u;
-  }
+  const int f = blockIdx.y * 8 + warp;
+  if (f >= F) return;
+  const float g = warp_dot<T, VEC>(h_s, wg + ((size_t)e * F + f) * W, W, lane);
+  const float u = warp_dot<T, VEC>(h_s, wu + ((size_t)e * F + f) * W, W, lane);
+  if (lane == 0) a[(size_t)item * F + f] = moe_act<ACT>(g) * u;
 }
 
-// grid (T, ceil(W / rows per block)).
-template <typename T>
+// grid (T, ceil(W / 8)); the token's activations [top, F] in shared memory.
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
 moe_down_kernel(const float* __restrict__ a, const T* __restrict__ wd, int W, int F, int top, const int32_t* __restrict__ idx,
-                const float* __restrict__ wt, float* __restrict__ y, long ldy, int c_per_block) {
+                const float* __restrict__ wt, float* __restrict__ y, long ldy) {
+  extern __shared__ float a_s[];
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < top * F; i += blockDim.x) a_s[i] = a[(size_t)t * top * F + i];
+  __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int c0 = blockIdx.y * c_per_block, c1 = min(W, c0 + c_per_block);
-  for (int c = c0 + warp; c < c1; c += 8) {
-    float total = 0.f;
-    for (int j = 0; j < top; ++j) {
-      const int e = idx[(size_t)t * top + j];
-      if (e < 0) continue;
-      const T* row = wd + ((size_t)e * W + c) * F;
-      const float* aj = a + ((size_t)t * top + j) * F;
-      float s = 0.f;
-      for (int i = lane; i < F; i += 32) s = fmaf(aj[i], to_f32(row[i]), s);
-      s = warp_sum(s);
-      total = fmaf(wt[(size_t)t * top + j], s, total);
-    }
-    if (lane == 0) y[(size_t)t * ldy + c] = total;
+  const int c = blockIdx.y * 8 + warp;
+  if (c >= W) return;
+  float total = 0.f;
+  for (int j = 0; j < top; ++j) {
+    const int e = idx[(size_t)t * top + j];
+    if (e < 0) continue;
+    const float s = warp_dot<T, VEC>(a_s + (size_t)j * F, wd + ((size_t)e * W + c) * F, F, lane);
+    total = fmaf(wt[(size_t)t * top + j], s, total);
   }
+  if (lane == 0) y[(size_t)t * ldy + c] = total;
 }
 
 }  // namespace llmi
@@ -131,25 +158,43 @@ LLMI_EXPORT int llmi_moe_route(const float* logits, long ld, int E, int top, con
   return launch_pdl(PDL_SMALL, moe_route_kernel, (n_tokens + 3) / 4, 128, 0, stream, logits, ld, E, top, tok_seq, idx, wt, n_tokens);
 }
 
+template <typename T, int ACT, bool VEC>
+static int launch_moe_up(const void* h, long ldh, const void* wg, const void* wu, int W, int F, int top, const int32_t* idx, float* a,
+                         int n_tokens, cudaStream_t stream) {
+  const size_t smem = (size_t)W * 4;
+  static PerDevice<size_t> allowed;
+  if (smem > 48 * 1024 && allowed.here() < smem) {
+    if (cudaFuncSetAttribute(moe_up_kernel<T, ACT, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return LLMI_ERR_BAD_SIZE;
+    allowed.here() = smem;
+  }
+  return launch_pdl(PDL_GEMM, moe_up_kernel<T, ACT, VEC>, dim3(n_tokens * top, (F + 7) / 8), dim3(256), smem, stream, (const T*)h, ldh,
+                    (const T*)wg, (const T*)wu, W, F, top, idx, a);
+}
+
+template <typename T, bool VEC>
+static int launch_moe_down(const float* a, const void* wd, int W, int F, int top, const int32_t* idx, const float* wt, float* y, long ldy,
+                           int n_tokens, cudaStream_t stream) {
+  const size_t smem = (size_t)top * F * 4;
+  static PerDevice<size_t> allowed;
+  if (smem > 48 * 1024 && allowed.here() < smem) {
+    if (cudaFuncSetAttribute(moe_down_kernel<T, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return LLMI_ERR_BAD_SIZE;
+    allowed.here() = smem;
+  }
+  return launch_pdl(PDL_GEMM, moe_down_kernel<T, VEC>, dim3(n_tokens, (W + 7) / 8), dim3(256), smem, stream, a, (const T*)wd, W, F, top,
+                    idx, wt, y, ldy);
+}
+
 LLMI_EXPORT int llmi_moe_up(int dtype, const void* h, long ldh, const void* wg, const void* wu, int W, int F, int top,
                             const int32_t* idx, float* a, int act, int n_tokens, cudaStream_t stream) {
-  if (n_tokens <= 0 || W <= 0 || F <= 0 || top <= 0 || (size_t)W * 4 > 160 * 1024) return LLMI_ERR_BAD_SIZE;
+  if (n_tokens <= 0 || W <= 0 || F <= 0 || top <= 0 || (size_t)W * 4 > 160 * 1024 || (F + 7) / 8 > 65535) return LLMI_ERR_BAD_SIZE;
   if (act != 0 && act != 1) return LLMI_ERR_UNSUPPORTED;
-  const int f_per_block = 64;
-  dim3 grid(n_tokens * top, (F + f_per_block - 1) / f_per_block);
-  if (grid.y > 65535) return LLMI_ERR_BAD_SIZE;
-  const size_t smem = (size_t)W * 4;
-#define LLMI_UP(T, ACT)                                                                                                   \
-  do {                                                                                                                    \
-    static PerDevice<size_t> allowed;                                                                                     \
-    if (smem > 48 * 1024 && allowed.here() < smem) {                                                                      \
-      if (cudaFuncSetAttribute(moe_up_kernel<T, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
-        return LLMI_ERR_BAD_SIZE;                                                                                         \
-      allowed.here() = smem;                                                                                              \
-    }                                                                                                                     \
-    return launch_pdl(PDL_GEMM, moe_up_kernel<T, ACT>, grid, dim3(256), smem, stream, (const T*)h, ldh, (const T*)wg,     \
-                      (const T*)wu, W, F, top, idx, a, f_per_block);                                                      \
-  } while (0)
+  const int esz = dtype == LLMI_DTYPE_F32 ? 4 : 2;
+  const bool vec = ((size_t)W * esz) % 16 == 0 && !((uintptr_t)wg & 15) && !((uintptr_t)wu & 15);
+#define LLMI_UP(T, ACT) \
+  return vec ? launch_moe_up<T, ACT, true>(h, ldh, wg, wu, W, F, top, idx, a, n_tokens, stream) \
+             : launch_moe_up<T, ACT, false>(h, ldh, wg, wu, W, F, top, idx, a, n_tokens, stream)
   if (dtype == LLMI_DTYPE_F32) { if (act == 0) LLMI_UP(float, 0); else LLMI_UP(float, 1); }
   if (dtype == LLMI_DTYPE_BF16) { if (act == 0) LLMI_UP(__nv_bfloat16, 0); else LLMI_UP(__nv_bfloat16, 1); }
 #undef LLMI_UP
@@ -158,15 +203,14 @@ LLMI_EXPORT int llmi_moe_up(int dtype, const void* h, long ldh, const void* wg, 
 
 LLMI_EXPORT int llmi_moe_down(int dtype, const float* a, const void* wd, int W, int F, int top, const int32_t* idx,
                               const float* wt, float* y, long ldy, int n_tokens, cudaStream_t stream) {
-  if (n_tokens <= 0 || W <= 0 || F <= 0 || top <= 0) return LLMI_ERR_BAD_SIZE;
-  const int c_per_block = 64;
-  dim3 grid(n_tokens, (W + c_per_block - 1) / c_per_block);
-  if (grid.y > 65535) return LLMI_ERR_BAD_SIZE;
+  if (n_tokens <= 0 || W <= 0 || F <= 0 || top <= 0 || (size_t)top * F * 4 > 160 * 1024 || (W + 7) / 8 > 65535) return LLMI_ERR_BAD_SIZE;
+  const int esz = dtype == LLMI_DTYPE_F32 ? 4 : 2;
+  const bool vec = ((size_t)F * esz) % 16 == 0 && !((uintptr_t)wd & 15);
   if (dtype == LLMI_DTYPE_F32)
-    return launch_pdl(PDL_GEMM, moe_down_kernel<float>, grid, dim3(256), 0, stream, a, (const float*)wd, W, F, top, idx, wt, y, ldy,
-                      c_per_block);
+    return vec ? launch_moe_down<float, true>(a, wd, W, F, top, idx, wt, y, ldy, n_tokens, stream)
+               : launch_moe_down<float, false>(a, wd, W, F, top, idx, wt, y, ldy, n_tokens, stream);
   if (dtype == LLMI_DTYPE_BF16)
-    return launch_pdl(PDL_GEMM, moe_down_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, a, (const __nv_bfloat16*)wd, W, F, top,
-                      idx, wt, y, ldy, c_per_block);
+    return vec ? launch_moe_down<__nv_bfloat16, true>(a, wd, W, F, top, idx, wt, y, ldy, n_tokens, stream)
+               : launch_moe_down<__nv_bfloat16, false>(a, wd, W, F, top, idx, wt, y, ldy, n_tokens, stream);
   return LLMI_ERR_BAD_DTYPE;
 }

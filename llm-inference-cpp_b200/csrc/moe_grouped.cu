@@ -24,7 +24,7 @@ __global__ void __launch_bounds__(1024)
 moe_group_kernel(const int32_t* __restrict__ idx, int n_items, int E, int32_t* __restrict__ offsets,
                  int32_t* __restrict__ sorted_items, int32_t* __restrict__ item_pos, int32_t* __restrict__ tile_expert,
                  int32_t* __restrict__ tile_row0, int32_t* __restrict__ n_tiles) {
-  __shared__ int cnt[256], start[257], cursor[256];
+  __shared__ int cnt[256], cursor[256];
   pdl_wait();
   pdl_launch_dependents();
   for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
@@ -37,7 +37,6 @@ moe_group_kernel(const int32_t* __restrict__ idx, int n_items, int E, int32_t* _
   if (threadIdx.x == 0) {
     int run = 0, tiles = 0;
     for (int e = 0; e < E; ++e) {
-      start[e] = run;
       cursor[e] = run;
       offsets[e] = run;
       for (int r = 0; r < cnt[e]; r += GB_M) {
@@ -47,7 +46,6 @@ moe_group_kernel(const int32_t* __restrict__ idx, int n_items, int E, int32_t* _
       }
       run += cnt[e];
     }
-    start[E] = run;
     offsets[E] = run;
     *n_tiles = tiles;
   }
@@ -65,22 +63,26 @@ moe_group_kernel(const int32_t* __restrict__ idx, int n_items, int E, int32_t* _
 
 // MODE 0: A rows are gathered token rows (item / top) of h, two weight matrices (gate, up), out = act(g) * u in bf16.
 // MODE 1: A rows are the sorted rows themselves, one weight matrix, out = fp32.
+// MODE 2: no experts — a batch of equal products, one per head (blockIdx.z): A rows are the M rows of x from column
+//         b * a_batch on, the weight is B0[b], out (bf16) goes to column b * o_batch on.
 template <int MODE, int ACT>
 __global__ void __launch_bounds__(128)
 moe_grouped_kernel(const __nv_bfloat16* __restrict__ A, long lda, const int32_t* __restrict__ sorted_items, int top,
                    const __nv_bfloat16* __restrict__ B0, const __nv_bfloat16* __restrict__ B1, int N, int K,
                    const int32_t* __restrict__ offsets, const int32_t* __restrict__ tile_expert,
-                   const int32_t* __restrict__ tile_row0, const int32_t* __restrict__ n_tiles, void* __restrict__ out, long ldo) {
+                   const int32_t* __restrict__ tile_row0, const int32_t* __restrict__ n_tiles, void* __restrict__ out, long ldo,
+                   int M, long a_batch, long o_batch) {
   extern __shared__ __align__(16) unsigned char gb_smem[];
   pdl_wait();
   pdl_launch_dependents();
   const int tile = blockIdx.x;
-  if (tile >= *n_tiles) return;
+  if (MODE != 2 && tile >= *n_tiles) return;
   constexpr int NB = MODE == 0 ? 2 : 1;
   constexpr int STAGE = (1 + NB) * GB_M * GB_LD;              // elements per stage (GB_M == GB_N)
   __nv_bfloat16* sm = reinterpret_cast<__nv_bfloat16*>(gb_smem);
-  const int e = tile_expert[tile], row0 = tile_row0[tile];
-  const int rows_here = min(GB_M, offsets[e + 1] - row0);
+  const int e = MODE == 2 ? (int)blockIdx.z : tile_expert[tile];
+  const int row0 = MODE == 2 ? tile * GB_M : tile_row0[tile];
+  const int rows_here = min(GB_M, (MODE == 2 ? M : offsets[e + 1]) - row0);
   const int n0 = blockIdx.y * GB_N;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
   const int wm = warp >> 1, wn = warp & 1;
@@ -97,7 +99,7 @@ moe_grouped_kernel(const __nv_bfloat16* __restrict__ A, long lda, const int32_t*
     const int r = slot_r[i];
     if (r < rows_here) {
       const long src_row = MODE == 0 ? (long)(sorted_items[row0 + r] / top) : (long)(row0 + r);
-      a_src[i] = A + src_row * lda;
+      a_src[i] = A + src_row * lda + (MODE == 2 ? (long)e * a_batch : 0L);
     } else {
       a_src[i] = nullptr;
     }
@@ -178,7 +180,11 @@ moe_grouped_kernel(const __nv_bfloat16* __restrict__ A, long lda, const int32_t*
         const int c = n0 + wn * 32 + nt * 8 + 2 * tq;
         if (c >= N) continue;
         const float v0 = acc[0][mi][nt][2 * half], v1 = acc[0][mi][nt][2 * half + 1];
-        if (MODE == 0) {
+        if (MODE == 2) {
+          __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)(row0 + r) * ldo + (size_t)e * o_batch + c;
+          if (c + 1 < N) *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(v0, v1);
+          else dst[0] = __float2bfloat16_rn(v0);
+        } else if (MODE == 0) {
           const float u0 = acc[NB - 1][mi][nt][2 * half], u1 = acc[NB - 1][mi][nt][2 * half + 1];
           const float a0 = ACT == 0 ? v0 / (1.0f + expf(-v0)) : 0.5f * v0 * (1.0f + tanhf(0.7978845608028654f * (v0 + 0.044715f * v0 * v0 * v0)));
           const float a1 = ACT == 0 ? v1 / (1.0f + expf(-v1)) : 0.5f * v1 * (1.0f + tanhf(0.7978845608028654f * (v1 + 0.044715f * v1 * v1 * v1)));
@@ -256,16 +262,32 @@ LLMI_EXPORT int llmi_moe_grouped(const void* h, long ldh, const void* wg, const 
   if (act == 0)
     rc = launch_pdl(PDL_GEMM, moe_grouped_kernel<0, 0>, grid_up, dim3(128), smem_up, stream, hb, ldh, (const int32_t*)sorted_items, top,
                     g, u, F, W, (const int32_t*)offsets, (const int32_t*)tile_expert, (const int32_t*)tile_row0,
-                    (const int32_t*)n_tiles, a_sorted, (long)F);
+                    (const int32_t*)n_tiles, a_sorted, (long)F, 0, 0L, 0L);
   else
     rc = launch_pdl(PDL_GEMM, moe_grouped_kernel<0, 1>, grid_up, dim3(128), smem_up, stream, hb, ldh, (const int32_t*)sorted_items, top,
                     g, u, F, W, (const int32_t*)offsets, (const int32_t*)tile_expert, (const int32_t*)tile_row0,
-                    (const int32_t*)n_tiles, a_sorted, (long)F);
+                    (const int32_t*)n_tiles, a_sorted, (long)F, 0, 0L, 0L);
   if (rc != LLMI_OK) return rc;
   rc = launch_pdl(PDL_GEMM, moe_grouped_kernel<1, 0>, grid_down, dim3(128), smem_down, stream, (const __nv_bfloat16*)a_sorted, (long)F,
                   (const int32_t*)sorted_items, top, d, d, W, F, (const int32_t*)offsets, (const int32_t*)tile_expert,
-                  (const int32_t*)tile_row0, (const int32_t*)n_tiles, (void*)y_sorted, (long)W);
+                  (const int32_t*)tile_row0, (const int32_t*)n_tiles, (void*)y_sorted, (long)W, 0, 0L, 0L);
   if (rc != LLMI_OK) return rc;
   return launch_pdl(PDL_SMALL, moe_combine_kernel, dim3(n_tokens), dim3(256), 0, stream, (const float*)y_sorted,
                     (const int32_t*)item_pos, wt, top, W, y, ldy);
+}
+
+// `batch` products of equal sizes on the tensor cores (bf16), one per head: out[:, b*by : b*by+N] = x[:, b*bx : b*bx+K] . w[b]^T,
+// w [batch, N, K] contiguous.  Needs K, ldx, bx multiples of 8 and even ldo, by (16-byte operand rows, 4-byte stores).
+LLMI_EXPORT int llmi_linear_heads_mma(const void* x, long ldx, long bx, const void* w, void* out, long ldo, long by, int batch, int M,
+                                      int N, int K, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0 || batch > 65535) return LLMI_ERR_BAD_SIZE;
+  if ((K % 8) || (ldx % 8) || (bx % 8) || (ldo % 2) || (by % 2) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 3))
+    return LLMI_ERR_ALIGN;
+  dim3 grid((M + GB_M - 1) / GB_M, (N + GB_N - 1) / GB_N, batch);
+  if (grid.y > 65535) return LLMI_ERR_BAD_SIZE;
+  const size_t smem = (size_t)GB_STAGES * 2 * GB_M * GB_LD * 2;
+  const __nv_bfloat16* wb = (const __nv_bfloat16*)w;
+  return launch_pdl(PDL_GEMM, moe_grouped_kernel<2, 0>, grid, dim3(128), smem, stream, (const __nv_bfloat16*)x, ldx,
+                    (const int32_t*)nullptr, 1, wb, wb, N, K, (const int32_t*)nullptr, (const int32_t*)nullptr, (const int32_t*)nullptr,
+                    (const int32_t*)nullptr, out, ldo, M, bx, by);
 }

@@ -153,7 +153,7 @@ def lib():
                      "llmi_sm_count", "llmi_dyt", "llmi_dyt_add", "llmi_stream_add", "llmi_linear_simt_batched",
                      "llmi_latent_prepare", "llmi_latent_q_rotate", "llmi_attention_latent", "llmi_delta_prepare",
                      "llmi_delta_conv_carry", "llmi_delta_recurrence", "llmi_delta_finish", "llmi_moe_route", "llmi_moe_up",
-                     "llmi_moe_down", "llmi_moe_grouped", "llmi_attention_latent_mma", "llmi_attention_latent_mma_supported"):
+                     "llmi_moe_down", "llmi_moe_grouped", "llmi_linear_heads_mma", "llmi_attention_latent_mma", "llmi_attention_latent_mma_supported"):
             getattr(l, name).restype = c_int
         l.llmi_gemm_tc_workspace.restype = c_long
         l.llmi_delta_state_floats.restype = c_long
@@ -864,15 +864,26 @@ def stream_add(x: torch.Tensor, add: torch.Tensor | None, vec: torch.Tensor | No
     _check("stream_add", lib().llmi_stream_add(_ptr(x), _ptr(add), _ptr(vec), c_int(T), c_int(W), _stream()))
 
 
+HEADS_MMA_MIN_TOKENS = 17      # from here on the per-head products of a step run on the tensor cores (bf16)
+
+
 def linear_batched(x: torch.Tensor, bx: int, w: torch.Tensor, out: torch.Tensor, by: int, K: int, mode: int = OUT_STORE) -> None:
     """``w.shape[0]`` products in one launch (one per head): out_b (mode) x_b . w[b]^T with x_b = x[:, b*bx : b*bx + K] and
-    out_b = out[:, b*by : b*by + N]; w [batch, N, K] contiguous.  fp32 FMA arithmetic in both types."""
+    out_b = out[:, b*by : b*by + N]; w [batch, N, K] contiguous.  fp32 FMA arithmetic for the 32-bit path and for a
+    handful of rows; bf16 products of more rows run as tensor-core tiles (bf16 in, fp32 accumulation)."""
     _need_cuda(x, w, out)
     B, N, Kw = w.shape
     M = x.shape[0]
     assert Kw == K and w.is_contiguous() and x.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == M and x.dtype == w.dtype
     assert (B - 1) * bx + K <= x.shape[1] and (B - 1) * by + N <= out.shape[1]
     assert out.dtype == (x.dtype if mode == OUT_STORE else torch.float32)
+    if (x.dtype == torch.bfloat16 and mode == OUT_STORE and M >= HEADS_MMA_MIN_TOKENS and not _FORCE_SIMT and K % 8 == 0
+            and bx % 8 == 0 and by % 2 == 0 and x.stride(0) % 8 == 0 and out.stride(0) % 2 == 0 and x.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0 and out.data_ptr() % 4 == 0):
+        _check("linear_heads_mma", lib().llmi_linear_heads_mma(
+            _ptr(x), c_long(x.stride(0)), c_long(bx), _ptr(w), _ptr(out), c_long(out.stride(0)), c_long(by), c_int(B), c_int(M),
+            c_int(N), c_int(K), _stream()))
+        return
     _check("linear_batched", lib().llmi_linear_simt_batched(
         c_int(_dtype_code(x)), _ptr(x), c_long(x.stride(0)), c_long(bx), _ptr(w), c_long(K), c_long(N * K), _ptr(out),
         c_long(out.stride(0)), c_long(by), c_int(B), c_int(M), c_int(N), c_int(K), c_int(mode), _stream()))

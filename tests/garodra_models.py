@@ -48,7 +48,7 @@ LOOPED = config(48, 101, [("delta", delta(2, 1, 16, 24, 3), dense(64)),
                           ("latent_attention", att(2, 24, 16, 8, 32, 12, rot_dims=16, base=500.0), dense(80))],
                 loop=(1, 3, 3), scale=1.5)
 LOOP_ONE = config(32, 64, [("latent_attention", att(2, 8, 8, 8, 12, 12), dense(48))], loop=(0, 1, 4))
-LOOP_ONCE = config(32, 64, [("delta", delta(2, 2, 32, 8, 2), None), ("latent_attention", att(2, 8, 8, 8, 12, 12), None)],
+LOOP_ONCE = config(32, 64, [("delta", delta(2, 2, 32, 16, 2), None), ("latent_attention", att(2, 8, 8, 8, 12, 12), None)],
                    loop=(0, 2, 1))
 # sizes of the kind the fast kernels take (multiples of 64), several layers
 WIDE = config(128, 300, [("latent_attention", att(4, 64, 32, 64, 128, 64), dense(256)),
