@@ -33,7 +33,7 @@ __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z));
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
 // One block per token.  prep: fp32 [T, Nc + 2H]: [ q^ | k^ | v (after convolution and silu) | beta | decay ].
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(512)
 delta_prepare_kernel(const float* __restrict__ proj, long ld, DeltaDims m, const float* __restrict__ conv_w,
                      const float* __restrict__ a_log, const float* __restrict__ dt_bias, const float* __restrict__ state,
                      const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ tok_pos,
@@ -192,16 +192,28 @@ delta_recurrence_kernel(const float* __restrict__ prep, long ldp, DeltaDims m, f
   }
 }
 
-// The same with FOUR lanes per column of S (D = 4 * DQ, the column's entries d = sub, sub + 4, ... in registers of lane
-// `sub`): a quarter of the serial work per token and of the registers, partial sums joined by two shuffles.  The
-// recurrence is a chain over the tokens, so the time of a prompt is tokens x (time of one token): this form is what
-// keeps that time short.
-template <int DQ>
-__global__ void __launch_bounds__(512)
+// The form for D = 32, 64, 128 and Dv a multiple of 16.  A thread holds FOUR neighbouring columns of S and an eighth of
+// their entries (lane `sub` of eight: d = 32 i + 4 sub + 0..3), in registers.  Every thread reads k and q from shared
+// memory, so the reads of a token are 2 D Dv / (columns per thread) floats: four columns per thread is what brings
+// them below the token's arithmetic (3 D Dv multiply-adds).  Partial sums over d are joined by three shuffles.
+// The recurrence is a chain over the tokens: the time of a prompt is tokens x (time of one token).
+//
+// What a token needs — k, q of the head's key head, v of the head, beta, g: 2*D + Dv + 2 floats — is copied into a ring
+// of DELTA_RING entries DELTA_RING - 1 tokens ahead (cp.async, no registers in between), so that no load's latency
+// lies on the chain from token to token; one barrier per token.
+constexpr int DELTA_RING = 8;
+
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(256)
 delta_recurrence_quad_kernel(const float* __restrict__ prep, long ldp, DeltaDims m, float* __restrict__ state,
                              const int32_t* __restrict__ seq_q_start, const int32_t* __restrict__ seq_slot,
                              float* __restrict__ o_raw, long ldo, int write_state) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   pdl_wait();
   pdl_launch_dependents();
   const int h = blockIdx.x, seq = blockIdx.y;
@@ -209,78 +221,113 @@ delta_recurrence_quad_kernel(const float* __restrict__ prep, long ldp, DeltaDims
   if (slot < 0) return;
   const int r0 = seq_q_start[seq], n = seq_q_start[seq + 1] - r0;
   if (n <= 0) return;
-  constexpr int D = 4 * DQ;
+  constexpr int NI = D / 32;                                 // chunks of four entries per lane
   const int Dv = m.Dv;
-  const int col = threadIdx.x >> 2, sub = threadIdx.x & 3;
-  const bool live = col < Dv;
-  const int j = live ? col : Dv - 1;
-  float* kq = sm;                                            // [2][2*D]: k then q of a token
+  const int cg = threadIdx.x >> 3, sub = threadIdx.x & 7;    // columns 4 cg .. 4 cg + 3 (the launcher gives 2 Dv threads)
   const int kh = h / (m.H / m.Hk);
-  float* S_g = state + (size_t)slot * m.state_floats() + (size_t)h * D * Dv;
-  float S_r[DQ];
+  float* S_g = state + (size_t)slot * m.state_floats() + (size_t)h * D * Dv + 4 * cg;
+  float4 S_r[NI][4];                                         // [chunk][entry of the chunk] . (x, y, z, w) = the four columns
 #pragma unroll
-  for (int i = 0; i < DQ; ++i) S_r[i] = S_g[(size_t)(sub + 4 * i) * Dv + j];
+  for (int i = 0; i < NI; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) S_r[i][e] = *reinterpret_cast<const float4*>(S_g + (size_t)(32 * i + 4 * sub + e) * Dv);
   const int Nc = m.n_conv();
-  // What the NEXT token needs is asked for before the current token is computed and put down after it, so that
-  // no load's latency lies on the chain from token to token: the entry of [k | q] this thread copies (the first 2*D
-  // threads; 4 * Dv >= 2 * D is checked by the launcher), and v, beta, g.
-  const bool copies = (int)threadIdx.x < 2 * D;
-  const size_t kq_off = (int)threadIdx.x < D ? (size_t)m.Hk * D + (size_t)kh * D + threadIdx.x : (size_t)kh * D + (threadIdx.x - D);
-  const size_t v_off = (size_t)m.n_qk() + (size_t)h * Dv + j;
-  const float* row = prep + (size_t)r0 * ldp;
-  if (copies) kq[threadIdx.x] = row[kq_off];
-  float v = row[v_off], beta = row[Nc + h], g = row[Nc + m.H + h];
-  for (int i = 0; i < n; ++i) {
-    __syncthreads();                                         // buffer i&1 is filled; the other one is read out
-    float n_kq = 0.f, n_v = 0.f, n_beta = 0.f, n_g = 0.f;
-    if (i + 1 < n) {
-      const float* nxt = prep + (size_t)(r0 + i + 1) * ldp;
-      if (copies) n_kq = nxt[kq_off];
-      n_v = nxt[v_off];
-      n_beta = nxt[Nc + h];
-      n_g = nxt[Nc + m.H + h];
+  const int n_in = 2 * D + Dv + 2, pitch = (n_in + 3) & ~3;
+  auto issue = [&](int i) {
+    float* dst = sm + (size_t)(i % DELTA_RING) * pitch;
+    const float* row = prep + (size_t)(r0 + i) * ldp;
+    for (int e = threadIdx.x; e < n_in; e += blockDim.x) {
+      size_t off;
+      if (e < D) off = (size_t)m.Hk * D + (size_t)kh * D + e;                   // k
+      else if (e < 2 * D) off = (size_t)kh * D + (e - D);                        // q
+      else if (e < 2 * D + Dv) off = (size_t)m.n_qk() + (size_t)h * Dv + (e - 2 * D);   // v
+      else off = e == 2 * D + Dv ? (size_t)(Nc + h) : (size_t)(Nc + m.H + h);    // beta, g
+      cp_async4(dst + e, row + off);
     }
-    const float* k = kq + (i & 1) * 2 * D + sub;
-    const float* q = k + D;
-    float p0 = 0.f, p1 = 0.f;
+  };
 #pragma unroll
-    for (int e = 0; e < DQ; e += 2) {
-      p0 = fmaf(S_r[e], k[4 * e], p0);
-      p1 = fmaf(S_r[e + 1], k[4 * e + 4], p1);
-    }
-    float sk = p0 + p1;
-    sk += __shfl_xor_sync(0xffffffffu, sk, 1);
-    sk += __shfl_xor_sync(0xffffffffu, sk, 2);
-    const float u = beta * (v - g * sk);
-    float o0 = 0.f, o1 = 0.f;
-#pragma unroll
-    for (int e = 0; e < DQ; e += 2) {
-      const float s0 = fmaf(k[4 * e], u, g * S_r[e]), s1 = fmaf(k[4 * e + 4], u, g * S_r[e + 1]);
-      S_r[e] = s0;
-      S_r[e + 1] = s1;
-      o0 = fmaf(s0, q[4 * e], o0);
-      o1 = fmaf(s1, q[4 * e + 4], o1);
-    }
-    float o = o0 + o1;
-    o += __shfl_xor_sync(0xffffffffu, o, 1);
-    o += __shfl_xor_sync(0xffffffffu, o, 2);
-    if (live && sub == 0) o_raw[(size_t)(r0 + i) * ldo + (size_t)h * Dv + j] = o;
-    if (copies && i + 1 < n) kq[((i + 1) & 1) * 2 * D + threadIdx.x] = n_kq;
-    v = n_v; beta = n_beta; g = n_g;
+  for (int s = 0; s < DELTA_RING - 1; ++s) {
+    if (s < n) issue(s);
+    asm volatile("cp.async.commit_group;" ::: "memory");
   }
-  if (live && write_state) {
+  for (int i = 0; i < n; ++i) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(DELTA_RING - 2) : "memory");
+    __syncthreads();                                         // token i's entry is there; token i-1's entry is read out
+    if (i + DELTA_RING - 1 < n) issue(i + DELTA_RING - 1);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const float* in = sm + (size_t)(i % DELTA_RING) * pitch;
+    float4 kk[NI], qq[NI];
 #pragma unroll
-    for (int i = 0; i < DQ; ++i) S_g[(size_t)(sub + 4 * i) * Dv + j] = S_r[i];
+    for (int c = 0; c < NI; ++c) {
+      kk[c] = *reinterpret_cast<const float4*>(in + 32 * c + 4 * sub);
+      qq[c] = *reinterpret_cast<const float4*>(in + D + 32 * c + 4 * sub);
+    }
+    const float4 v = *reinterpret_cast<const float4*>(in + 2 * D + 4 * cg);
+    const float beta = in[2 * D + Dv], g = in[2 * D + Dv + 1];
+    float4 sk = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int c = 0; c < NI; ++c) {
+      const float ke[4] = {kk[c].x, kk[c].y, kk[c].z, kk[c].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        sk.x = fmaf(S_r[c][e].x, ke[e], sk.x);
+        sk.y = fmaf(S_r[c][e].y, ke[e], sk.y);
+        sk.z = fmaf(S_r[c][e].z, ke[e], sk.z);
+        sk.w = fmaf(S_r[c][e].w, ke[e], sk.w);
+      }
+    }
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+      sk.x += __shfl_xor_sync(0xffffffffu, sk.x, o);
+      sk.y += __shfl_xor_sync(0xffffffffu, sk.y, o);
+      sk.z += __shfl_xor_sync(0xffffffffu, sk.z, o);
+      sk.w += __shfl_xor_sync(0xffffffffu, sk.w, o);
+    }
+    const float4 u = make_float4(beta * (v.x - g * sk.x), beta * (v.y - g * sk.y), beta * (v.z - g * sk.z), beta * (v.w - g * sk.w));
+    float4 o4 = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int c = 0; c < NI; ++c) {
+      const float ke[4] = {kk[c].x, kk[c].y, kk[c].z, kk[c].w};
+      const float qe[4] = {qq[c].x, qq[c].y, qq[c].z, qq[c].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float4 s = S_r[c][e];
+        s.x = fmaf(ke[e], u.x, g * s.x);
+        s.y = fmaf(ke[e], u.y, g * s.y);
+        s.z = fmaf(ke[e], u.z, g * s.z);
+        s.w = fmaf(ke[e], u.w, g * s.w);
+        S_r[c][e] = s;
+        o4.x = fmaf(s.x, qe[e], o4.x);
+        o4.y = fmaf(s.y, qe[e], o4.y);
+        o4.z = fmaf(s.z, qe[e], o4.z);
+        o4.w = fmaf(s.w, qe[e], o4.w);
+      }
+    }
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+      o4.x += __shfl_xor_sync(0xffffffffu, o4.x, o);
+      o4.y += __shfl_xor_sync(0xffffffffu, o4.y, o);
+      o4.z += __shfl_xor_sync(0xffffffffu, o4.z, o);
+      o4.w += __shfl_xor_sync(0xffffffffu, o4.w, o);
+    }
+    if (sub == 0) *reinterpret_cast<float4*>(o_raw + (size_t)(r0 + i) * ldo + (size_t)h * Dv + 4 * cg) = o4;
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  if (write_state) {
+#pragma unroll
+    for (int i = 0; i < NI; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) *reinterpret_cast<float4*>(S_g + (size_t)(32 * i + 4 * sub + e) * Dv) = S_r[i][e];
   }
 }
 
-template <int DQ>
+template <int D>
 int launch_delta_recurrence_quad(const float* prep, long ldp, DeltaDims m, float* state, const int32_t* seq_q_start,
                                  const int32_t* seq_slot, float* o_raw, long ldo, int n_seqs, int write_state,
                                  cudaStream_t stream) {
-  const int threads = (4 * m.Dv + 31) / 32 * 32;
-  return launch_pdl(PDL_ATTENTION, delta_recurrence_quad_kernel<DQ>, dim3(m.H, n_seqs), dim3(threads), (size_t)16 * DQ * sizeof(float),
-                    stream, prep, ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, write_state);
+  const size_t smem = (size_t)DELTA_RING * ((2 * D + m.Dv + 2 + 3) & ~3) * sizeof(float);
+  return launch_pdl(PDL_ATTENTION, delta_recurrence_quad_kernel<D>, dim3(m.H, n_seqs), dim3(2 * m.Dv), smem, stream, prep, ldp, m,
+                    state, seq_q_start, seq_slot, o_raw, ldo, write_state);
 }
 
 // One warp per (token, head): out = o / sqrt(mean(o^2) + eps) * w * silu(gate).
@@ -345,7 +392,9 @@ LLMI_EXPORT int llmi_delta_prepare(const float* proj, long ld, int H, int Hk, in
   if (n_tokens <= 0 || !delta_dims_ok(m)) return LLMI_ERR_BAD_SIZE;
   const size_t smem = (size_t)m.n_qk() * sizeof(float);
   if (smem > 48 * 1024) return LLMI_ERR_BAD_SIZE;
-  return launch_pdl(PDL_SMALL, delta_prepare_kernel, n_tokens, 128, smem, stream, proj, ld, m, conv_w, a_log, dt_bias, state,
+  // a handful of tokens: many threads a token, so that the few blocks' loads overlap; a prompt: many blocks already
+  const int threads = n_tokens <= 64 ? 512 : 128;
+  return launch_pdl(PDL_SMALL, delta_prepare_kernel, n_tokens, threads, smem, stream, proj, ld, m, conv_w, a_log, dt_bias, state,
                     tok_seq, tok_pos, seq_q_start, seq_slot, prep, ldp);
 }
 
@@ -364,10 +413,12 @@ LLMI_EXPORT int llmi_delta_recurrence(const float* prep, long ldp, int H, int Hk
                                       int write_state, cudaStream_t stream) {
   const DeltaDims m{H, Hk, D, Dv, taps};
   if (n_seqs <= 0 || n_seqs > 65535 || !delta_dims_ok(m)) return LLMI_ERR_BAD_SIZE;
-  if (Dv <= 128 && 4 * ((Dv + 7) / 8 * 8) >= 2 * D) {          // (the block's threads also copy [k | q]: 2 * D entries)
-    if (D == 32) return launch_delta_recurrence_quad<8>(prep, ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, n_seqs, write_state, stream);
-    if (D == 64) return launch_delta_recurrence_quad<16>(prep, ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, n_seqs, write_state, stream);
-    if (D == 128) return launch_delta_recurrence_quad<32>(prep, ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, n_seqs, write_state, stream);
+  // (16-byte accesses: state rows, o rows and the ring's v entries must be 16-byte aligned)
+  if (Dv <= 128 && Dv % 16 == 0 && ldo % 4 == 0 && !((uintptr_t)state & 15) && !((uintptr_t)o_raw & 15) &&
+      DeltaDims{H, Hk, D, Dv, taps}.state_floats() % 4 == 0) {
+    if (D == 32) return launch_delta_recurrence_quad<32>(prep, ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, n_seqs, write_state, stream);
+    if (D == 64) return launch_delta_recurrence_quad<64>(prep, ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, n_seqs, write_state, stream);
+    if (D == 128) return launch_delta_recurrence_quad<128>(prep, ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, n_seqs, write_state, stream);
   }
   if ((size_t)D * ((Dv + 31) / 32 * 32) * 4 + 16 * (size_t)D > 200 * 1024) return LLMI_ERR_BAD_SIZE;
   return launch_delta_recurrence<0>(prep, ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, n_seqs, write_state, stream);

@@ -38,20 +38,22 @@ struct LatentMmaArgs {
   float* ws_ml;                 // [T, H, splits, 2]
 };
 
-// NT = C / 32: the 8-column tiles of O that one warp owns.
-template <int NT>
-__global__ void __launch_bounds__(LM_WARPS * 32)
+// NT = C / 32: the 8-column tiles of O that one warp owns.  RG: groups of 16 query rows (of four warps each) that share
+// the block's pages — 1 for single tokens, 2 for prompts, where a page then feeds twice the rows per load.
+template <int NT, int RG>
+__global__ void __launch_bounds__(LM_WARPS * 32 * RG)
 attention_latent_mma_kernel(const LatentMmaArgs a) {
   extern __shared__ __align__(16) unsigned char lm_smem[];
   pdl_wait();
   pdl_launch_dependents();
   const int Dk = a.C + a.R, ldk = Dk + LM_PAD;               // padded pitch: ldmatrix rows fall on different banks
-  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(lm_smem);                 // [16][ldk]
-  __nv_bfloat16* k_s = q_s + LM_ROWS * ldk;                                        // [2][64][ldk]
-  __nv_bfloat16* p_s = k_s + 2 * LM_KEYS * ldk;                                    // [16][64 + 8]
-  float* max_s = reinterpret_cast<float*>(p_s + LM_ROWS * (LM_KEYS + LM_PAD));     // [4][16]
-  float* sum_s = max_s + LM_WARPS * LM_ROWS;                                       // [4][16]
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(lm_smem);                 // [RG * 16][ldk]
+  __nv_bfloat16* k_s = q_s + RG * LM_ROWS * ldk;                                   // [2][64][ldk]
+  const int rg = threadIdx.x >> 7;                                                 // my group of 16 rows
+  __nv_bfloat16* p_s = k_s + 2 * LM_KEYS * ldk + rg * LM_ROWS * (LM_KEYS + LM_PAD);         // [RG][16][64 + 8]: my group's
+  float* max_s = reinterpret_cast<float*>(k_s + 2 * LM_KEYS * ldk + RG * LM_ROWS * (LM_KEYS + LM_PAD)) + rg * LM_WARPS * LM_ROWS;   // [RG][4][16]
+  float* sum_s = max_s + RG * LM_WARPS * LM_ROWS;                                  // [RG][4][16]
+  const int warp = (threadIdx.x >> 5) & 3, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
   const int t0 = blockIdx.x * a.tokens_per_block, h0 = blockIdx.y * a.heads_per_block, split = blockIdx.z;
   const int t_last = min(t0 + a.tokens_per_block, a.n_tokens) - 1;
 
@@ -65,7 +67,7 @@ attention_latent_mma_kernel(const LatentMmaArgs a) {
   int row_tok[2], row_head[2];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    const int r = g + 8 * i;
+    const int r = rg * LM_ROWS + g + 8 * i;
     row_tok[i] = t0 + r / a.heads_per_block;
     row_head[i] = h0 + r % a.heads_per_block;
   }
@@ -83,7 +85,7 @@ attention_latent_mma_kernel(const LatentMmaArgs a) {
       row_pos[i] = ok ? a.tok_pos[row_tok[i]] : -1;
     }
     const int chunks = Dk / 8;
-    for (int idx = threadIdx.x; idx < LM_ROWS * chunks; idx += blockDim.x) {
+    for (int idx = threadIdx.x; idx < RG * LM_ROWS * chunks; idx += blockDim.x) {
       const int r = idx / chunks, c8 = idx - r * chunks;
       const int t = t0 + r / a.heads_per_block, h = h0 + r % a.heads_per_block;
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -121,21 +123,40 @@ attention_latent_mma_kernel(const LatentMmaArgs a) {
       if (pg + 1 < pg_hi) fetch(pg + 1, buf ^ 1);
       const __nv_bfloat16* kt = k_s + (size_t)buf * LM_KEYS * ldk;
 
-      // scores of my warp's 16 keys
+      // scores of my warp's 16 keys; the k steps go round four sets of accumulators, so that the chain of dependent
+      // products is a quarter as long
+      float s4[4][2][4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s4[c][j][e] = 0.f;
+      const __nv_bfloat16* a_ptr = q_s + (rg * LM_ROWS + (lane & 15)) * ldk + (lane >> 4) * 8;
+      const __nv_bfloat16* b_ptr = kt + (16 * warp + (lane >> 4) * 8 + (lane & 7)) * ldk + ((lane >> 3) & 1) * 8;
+      int k0 = 0;
+      for (; k0 + 64 <= Dk; k0 += 64) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t af[4], bf[4];
+          ldsm_x4(af, a_ptr + k0 + 16 * c);
+          ldsm_x4(bf, b_ptr + k0 + 16 * c);
+          mma_bf16(s4[c][0], af, bf[0], bf[1]);
+          mma_bf16(s4[c][1], af, bf[2], bf[3]);
+        }
+      }
+      for (; k0 < Dk; k0 += 16) {
+        uint32_t af[4], bf[4];
+        ldsm_x4(af, a_ptr + k0);
+        ldsm_x4(bf, b_ptr + k0);
+        mma_bf16(s4[0][0], af, bf[0], bf[1]);
+        mma_bf16(s4[0][1], af, bf[2], bf[3]);
+      }
       float s[2][4];
 #pragma unroll
       for (int j = 0; j < 2; ++j)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
-      const __nv_bfloat16* a_ptr = q_s + (lane & 15) * ldk + (lane >> 4) * 8;
-      const __nv_bfloat16* b_ptr = kt + (16 * warp + (lane >> 4) * 8 + (lane & 7)) * ldk + ((lane >> 3) & 1) * 8;
-      for (int k0 = 0; k0 < Dk; k0 += 16) {
-        uint32_t af[4], bf[4];
-        ldsm_x4(af, a_ptr + k0);
-        ldsm_x4(bf, b_ptr + k0);
-        mma_bf16(s[0], af, bf[0], bf[1]);
-        mma_bf16(s[1], af, bf[2], bf[3]);
-      }
+        for (int e = 0; e < 4; ++e) s[j][e] = (s4[0][j][e] + s4[1][j][e]) + (s4[2][j][e] + s4[3][j][e]);
       // mask, and the maximum of each of my rows over my warp's keys
       const int key0 = pg * LM_KEYS + 16 * warp + 2 * tq;
       float mx[2] = {-INFINITY, -INFINITY};
@@ -246,40 +267,60 @@ attention_latent_mma_kernel(const LatentMmaArgs a) {
           for (int c = threadIdx.x; c < a.C; c += blockDim.x) a.out[(size_t)t * a.ldo + (size_t)hh * a.C + c] = __float2bfloat16_rn(0.f);
 }
 
-// One warp per (token, head): joins the cuts.  out = sum_s e^(m_s - M) O_s / sum_s e^(m_s - M) l_s.
+// One block per (token, head): joins the cuts.  out = sum_s e^(m_s - M) O_s / sum_s e^(m_s - M) l_s.  The weights
+// e^(m_s - M) / denominator are made once, in shared memory; every thread then adds its columns over the cuts with
+// independent loads.
+constexpr int LM_MAX_SPLITS = 512;
 __global__ void __launch_bounds__(128)
 attention_latent_join_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml, __nv_bfloat16* __restrict__ out,
-                             long ldo, const int32_t* __restrict__ tok_seq, int n_heads, int C, int splits, long n_items) {
+                             long ldo, const int32_t* __restrict__ tok_seq, int n_heads, int C, int splits) {
+  __shared__ float w_s[LM_MAX_SPLITS];
+  __shared__ float red[32];
   pdl_wait();
   pdl_launch_dependents();
-  const long item = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (item >= n_items) return;
-  const int lane = threadIdx.x & 31;
+  const long item = blockIdx.x;
   const int t = (int)(item / n_heads), h = (int)(item - (long)t * n_heads);
   if (tok_seq[t] < 0) return;                                 // (zeros were written by the first kernel)
   const float* ml = ws_ml + (size_t)item * splits * 2;
   float M = -INFINITY;
-  for (int s = 0; s < splits; ++s) M = fmaxf(M, ml[2 * s]);
-  float denom = 0.f;
-  for (int s = 0; s < splits; ++s) denom += ml[2 * s] == -INFINITY ? 0.f : expf(ml[2 * s] - M) * ml[2 * s + 1];
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, ml[2 * s]);   // (the same few words for every thread: served by the cache)
+  float part = 0.f;
+  for (int s = threadIdx.x; s < splits; s += blockDim.x) {
+    const float m = ml[2 * s];
+    const float w = m == -INFINITY ? 0.f : expf(m - M);
+    w_s[s] = w;
+    part += w * ml[2 * s + 1];
+  }
+  const float denom = block_sum(part, red);
   const float inv = 1.0f / denom;
-  for (int c = lane; c < C; c += 32) {
-    float acc = 0.f;
-    for (int s = 0; s < splits; ++s)
-      if (ml[2 * s] != -INFINITY) acc = fmaf(expf(ml[2 * s] - M), ws_o[((size_t)item * splits + s) * C + c], acc);
-    out[(size_t)t * ldo + (size_t)h * C + c] = __float2bfloat16_rn(acc * inv);
+  const float* o = ws_o + (size_t)item * splits * C;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    int s = 0;
+    for (; s + 4 <= splits; s += 4) {
+      a0 = fmaf(w_s[s], o[(size_t)s * C + c], a0);
+      a1 = fmaf(w_s[s + 1], o[(size_t)(s + 1) * C + c], a1);
+      a2 = fmaf(w_s[s + 2], o[(size_t)(s + 2) * C + c], a2);
+      a3 = fmaf(w_s[s + 3], o[(size_t)(s + 3) * C + c], a3);
+    }
+    for (; s < splits; ++s) a0 = fmaf(w_s[s], o[(size_t)s * C + c], a0);
+    out[(size_t)t * ldo + (size_t)h * C + c] = __float2bfloat16_rn(((a0 + a1) + (a2 + a3)) * inv);
   }
 }
 
-template <int NT>
-int launch_latent_mma(const LatentMmaArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
+template <int NT, int RG>
+int launch_latent_mma_rg(const LatentMmaArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
   static PerDevice<size_t> allowed;
   if (smem > 48 * 1024 && allowed.here() < smem) {
-    if (cudaFuncSetAttribute(attention_latent_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(attention_latent_mma_kernel<NT, RG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return LLMI_ERR_BAD_SIZE;
     allowed.here() = smem;
   }
-  return launch_pdl(PDL_ATTENTION, attention_latent_mma_kernel<NT>, grid, dim3(LM_WARPS * 32), smem, stream, a);
+  return launch_pdl(PDL_ATTENTION, attention_latent_mma_kernel<NT, RG>, grid, dim3(LM_WARPS * 32 * RG), smem, stream, a);
+}
+template <int NT>
+int launch_latent_mma(const LatentMmaArgs& a, dim3 grid, size_t smem, int row_groups, cudaStream_t stream) {
+  return row_groups == 2 ? launch_latent_mma_rg<NT, 2>(a, grid, smem, stream) : launch_latent_mma_rg<NT, 1>(a, grid, smem, stream);
 }
 
 }  // namespace llmi
@@ -298,10 +339,10 @@ LLMI_EXPORT long llmi_attention_latent_mma_workspace(int n_tokens, int n_heads, 
 LLMI_EXPORT int llmi_attention_latent_mma(const void* qa, long ldq, void* out, long ldo, const void* cache,
                                           const int32_t* tok_seq, const int32_t* tok_pos, const int32_t* seq_pages,
                                           int pages_stride, int page_size, int n_tokens, int n_heads, int C, int R, float scale,
-                                          int splits, int pages_per_split, float* workspace, long workspace_floats,
-                                          cudaStream_t stream) {
+                                          int splits, int pages_per_split, int row_groups, float* workspace,
+                                          long workspace_floats, cudaStream_t stream) {
   if (n_tokens <= 0 || n_heads <= 0 || !llmi_attention_latent_mma_supported(C, R, page_size)) return LLMI_ERR_UNSUPPORTED;
-  if (splits < 1 || splits > 65535 || pages_per_split < 1) return LLMI_ERR_BAD_SIZE;
+  if (splits < 1 || splits > LM_MAX_SPLITS || pages_per_split < 1 || (row_groups != 1 && row_groups != 2)) return LLMI_ERR_BAD_SIZE;
   if (((uintptr_t)qa & 15) || ((uintptr_t)cache & 15) || (ldq % 8) || ((uintptr_t)out & 3) || (ldo % 2)) return LLMI_ERR_ALIGN;
   if (splits > 1 && (!workspace || workspace_floats < llmi_attention_latent_mma_workspace(n_tokens, n_heads, C, splits)))
     return LLMI_ERR_BAD_SIZE;
@@ -311,26 +352,27 @@ LLMI_EXPORT int llmi_attention_latent_mma(const void* qa, long ldq, void* out, l
   a.qa = (const __nv_bfloat16*)qa; a.ldq = ldq; a.out = (__nv_bfloat16*)out; a.ldo = ldo; a.cache = (const __nv_bfloat16*)cache;
   a.tok_seq = tok_seq; a.tok_pos = tok_pos; a.seq_pages = seq_pages; a.pages_stride = pages_stride;
   a.n_tokens = n_tokens; a.n_heads = n_heads; a.C = C; a.R = R;
-  a.heads_per_block = hpb; a.tokens_per_block = LM_ROWS / hpb;
+  a.heads_per_block = hpb; a.tokens_per_block = row_groups * LM_ROWS / hpb;
   a.splits = splits; a.pages_per_split = pages_per_split; a.scale = scale;
   a.ws_o = workspace;
   a.ws_ml = workspace ? workspace + (size_t)n_tokens * n_heads * splits * C : nullptr;
   dim3 grid((n_tokens + a.tokens_per_block - 1) / a.tokens_per_block, (n_heads + hpb - 1) / hpb, splits);
   if (grid.y > 65535) return LLMI_ERR_BAD_SIZE;
   const int ldk = C + R + LM_PAD;
-  const size_t smem = (size_t)(LM_ROWS + 2 * LM_KEYS) * ldk * 2 + (size_t)LM_ROWS * (LM_KEYS + LM_PAD) * 2 + 2 * LM_WARPS * LM_ROWS * 4;
+  const size_t smem = (size_t)(row_groups * LM_ROWS + 2 * LM_KEYS) * ldk * 2 +
+                      (size_t)row_groups * (LM_ROWS * (LM_KEYS + LM_PAD) * 2 + 2 * LM_WARPS * LM_ROWS * 4);
   int rc;
   switch (C / 32) {
-    case 2: rc = launch_latent_mma<2>(a, grid, smem, stream); break;
-    case 4: rc = launch_latent_mma<4>(a, grid, smem, stream); break;
-    case 6: rc = launch_latent_mma<6>(a, grid, smem, stream); break;
-    case 8: rc = launch_latent_mma<8>(a, grid, smem, stream); break;
-    case 12: rc = launch_latent_mma<12>(a, grid, smem, stream); break;
-    case 16: rc = launch_latent_mma<16>(a, grid, smem, stream); break;
+    case 2: rc = launch_latent_mma<2>(a, grid, smem, row_groups, stream); break;
+    case 4: rc = launch_latent_mma<4>(a, grid, smem, row_groups, stream); break;
+    case 6: rc = launch_latent_mma<6>(a, grid, smem, row_groups, stream); break;
+    case 8: rc = launch_latent_mma<8>(a, grid, smem, row_groups, stream); break;
+    case 12: rc = launch_latent_mma<12>(a, grid, smem, row_groups, stream); break;
+    case 16: rc = launch_latent_mma<16>(a, grid, smem, row_groups, stream); break;
     default: return LLMI_ERR_UNSUPPORTED;
   }
   if (rc != LLMI_OK || splits == 1) return rc;
   const long items = (long)n_tokens * n_heads;
-  return launch_pdl(PDL_SMALL, attention_latent_join_kernel, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream,
-                    (const float*)a.ws_o, (const float*)a.ws_ml, (__nv_bfloat16*)out, ldo, tok_seq, n_heads, C, splits, items);
+  return launch_pdl(PDL_SMALL, attention_latent_join_kernel, dim3((unsigned)items), dim3(128), 0, stream, (const float*)a.ws_o,
+                    (const float*)a.ws_ml, (__nv_bfloat16*)out, ldo, tok_seq, n_heads, C, splits);
 }

@@ -864,7 +864,7 @@ def stream_add(x: torch.Tensor, add: torch.Tensor | None, vec: torch.Tensor | No
     _check("stream_add", lib().llmi_stream_add(_ptr(x), _ptr(add), _ptr(vec), c_int(T), c_int(W), _stream()))
 
 
-HEADS_MMA_MIN_TOKENS = 17      # from here on the per-head products of a step run on the tensor cores (bf16)
+HEADS_MMA_MIN_TOKENS = int(os.environ.get("LLMI_HEADS_MMA_MIN", "1"))      # from here on the per-head products of a step run on the tensor cores (bf16)
 
 
 def linear_batched(x: torch.Tensor, bx: int, w: torch.Tensor, out: torch.Tensor, by: int, K: int, mode: int = OUT_STORE) -> None:
@@ -931,7 +931,7 @@ def latent_attention_plan(ctx, n_tokens: int, n_pages: int, H: int) -> tuple:
     while hpb < H and hpb < 16:
         hpb *= 2
     blocks = -(-n_tokens // (16 // hpb)) * -(-H // hpb)
-    want = max(1, min(n_pages, -(-2 * sm_count() // blocks)))
+    want = max(1, min(n_pages, 512, -(-2 * sm_count() // blocks)))
     pps = -(-n_pages // want)
     return -(-n_pages // pps), pps
 
@@ -954,7 +954,7 @@ def attention_latent(qa: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
         _check("attention_latent_mma", lib().llmi_attention_latent_mma(
             _ptr(qa), c_long(qa.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(cache), _ptr(ctx.tok_seq), _ptr(ctx.tok_pos),
             _ptr(seq_pages), c_int(seq_pages.stride(0)), c_int(page_size), c_int(T), c_int(H), c_int(C), c_int(R), c_float(scale),
-            c_int(splits), c_int(pps), _ptr(ws), c_long(n_ws), _stream()))
+            c_int(splits), c_int(pps), c_int(1 if ctx.decode else 2), _ptr(ws), c_long(n_ws), _stream()))
         return
     _check("attention_latent", lib().llmi_attention_latent(
         c_int(_dtype_code(qa)), _ptr(qa), c_long(qa.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(cache), _ptr(ctx.tok_seq),
@@ -1040,7 +1040,7 @@ def moe_experts_streamed(h: torch.Tensor, w_gate, w_up, w_down, idx, wt, act: in
                                        _ptr(wt), _ptr(y), c_long(y.stride(0)), c_int(T), _stream()))
 
 
-MOE_GROUPED_MIN_TOKENS = int(os.environ.get("LLMI_MOE_GROUPED_MIN", "33"))
+MOE_GROUPED_MIN_TOKENS = int(os.environ.get("LLMI_MOE_GROUPED_MIN", "4"))
 
 
 def moe_grouped_applies(h: torch.Tensor, W: int, F: int, E: int) -> bool:
