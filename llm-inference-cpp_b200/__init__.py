@@ -1,5 +1,5 @@
 """A small B200-native model library with generation of its own, for the Llama / SmolLM2
-dense decoder: from a model folder (or a configuration and a seed) to generated tokens on
+dense decoder and the Garodra design (config.json picks the recipe): from a model folder (or a configuration and a seed) to generated tokens on
 one GPU, on hand-written sm_100a kernels.
 
 Python entry points::
@@ -11,7 +11,7 @@ Python entry points::
 """
 from . import models  # noqa: F401  (registers the architectures)
 from .cache import CacheError, SequenceCache  # noqa: F401
-from .config import ConfigError, LlamaConfig, parse_config, register_architecture  # noqa: F401
+from .config import ConfigError, GarodraConfig, LlamaConfig, parse_config, register_architecture  # noqa: F401
 from .engine import Model, SequenceStep, StepError, load_model, random_model  # noqa: F401
 from .engine.generate import generate  # noqa: F401
 from .parts import register_part  # noqa: F401

@@ -74,6 +74,19 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // size selects.
 __device__ __forceinline__ float rot_lo(float a, float b, float c, float s) { return __fmaf_rn(a, c, -__fmul_rn(b, s)); }
 __device__ __forceinline__ float rot_hi(float a, float b, float c, float s) { return __fmaf_rn(b, c, __fmul_rn(a, s)); }
+// Callers may ask for mode 4: the gated epilogue of OUT_SWIGLU with the tanh form of GELU as the gate's activation
+// (the launchers turn it into OUT_SWIGLU with `act` = 1).
+constexpr int OUT_GEGLU_REQUEST = 4;
+
+// act(gate) * up of the gated epilogues.  act 0: silu; 1: 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).  The
+// result is rounded to bf16: the fast exponential and divide suffice (tanh(z) = 1 - 2 / (1 + e^(2z))).
+__device__ __forceinline__ float gated_value(float g, float u, int act) {
+  if (act == 0) return __fdividef(g, 1.0f + __expf(-g)) * u;
+  const float z = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+  const float th = 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * z));
+  return 0.5f * g * (1.0f + th) * u;
+}
+
 // Facts and one-time set-up per device.  A process may drive several GPUs, and a function attribute (the
 // dynamic shared memory a kernel may ask for) or a count derived from the device (how many blocks are
 // resident at once) belongs to the device that was current when it was set or read.

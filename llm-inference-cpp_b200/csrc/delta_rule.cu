@@ -112,7 +112,7 @@ delta_conv_carry_kernel(const float* __restrict__ proj, long ld, DeltaDims m, fl
 // registers; DREG == 0: any D, the column lives in shared memory (S_s[d][j]: no two threads share a bank).
 // k and q of the next token are fetched while the current one is computed (two buffers, one barrier per token).
 template <int DREG>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 delta_recurrence_kernel(const float* __restrict__ prep, long ldp, DeltaDims m, float* __restrict__ state,
                         const int32_t* __restrict__ seq_q_start, const int32_t* __restrict__ seq_slot,
                         float* __restrict__ o_raw, long ldo, int write_state) {
@@ -196,7 +196,9 @@ delta_recurrence_kernel(const float* __restrict__ prep, long ldp, DeltaDims m, f
 // their entries (lane `sub` of eight: d = 32 i + 4 sub + 0..3), in registers.  Every thread reads k and q from shared
 // memory, so the reads of a token are 2 D Dv / (columns per thread) floats: four columns per thread is what brings
 // them below the token's arithmetic (3 D Dv multiply-adds).  Partial sums over d are joined by three shuffles.
-// The recurrence is a chain over the tokens: the time of a prompt is tokens x (time of one token).
+// The recurrence is a chain over the tokens: the time of a prompt is tokens x (time of one token).  Columns are
+// independent, so a head's columns are cut into slices of 32 (or 16) and every slice is a block of its own
+// (blockIdx.z): more SMs at work on one prompt, and fewer instructions per token on each.
 //
 // What a token needs — k, q of the head's key head, v of the head, beta, g: 2*D + Dv + 2 floats — is copied into a ring
 // of DELTA_RING entries DELTA_RING - 1 tokens ahead (cp.async, no registers in between), so that no load's latency
@@ -209,7 +211,7 @@ __device__ __forceinline__ void cp_async4(void* dst, const void* src) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(64)
 delta_recurrence_quad_kernel(const float* __restrict__ prep, long ldp, DeltaDims m, float* __restrict__ state,
                              const int32_t* __restrict__ seq_q_start, const int32_t* __restrict__ seq_slot,
                              float* __restrict__ o_raw, long ldo, int write_state) {
@@ -223,16 +225,18 @@ delta_recurrence_quad_kernel(const float* __restrict__ prep, long ldp, DeltaDims
   if (n <= 0) return;
   constexpr int NI = D / 32;                                 // chunks of four entries per lane
   const int Dv = m.Dv;
-  const int cg = threadIdx.x >> 3, sub = threadIdx.x & 7;    // columns 4 cg .. 4 cg + 3 (the launcher gives 2 Dv threads)
+  const int CB = blockDim.x >> 1;                            // columns of this block's slice (the launcher gives 2 CB threads)
+  const int cg = threadIdx.x >> 3, sub = threadIdx.x & 7;    // my columns: col0 .. col0 + 3
+  const int col0 = blockIdx.z * CB + 4 * cg;
   const int kh = h / (m.H / m.Hk);
-  float* S_g = state + (size_t)slot * m.state_floats() + (size_t)h * D * Dv + 4 * cg;
+  float* S_g = state + (size_t)slot * m.state_floats() + (size_t)h * D * Dv + col0;
   float4 S_r[NI][4];                                         // [chunk][entry of the chunk] . (x, y, z, w) = the four columns
 #pragma unroll
   for (int i = 0; i < NI; ++i)
 #pragma unroll
     for (int e = 0; e < 4; ++e) S_r[i][e] = *reinterpret_cast<const float4*>(S_g + (size_t)(32 * i + 4 * sub + e) * Dv);
   const int Nc = m.n_conv();
-  const int n_in = 2 * D + Dv + 2, pitch = (n_in + 3) & ~3;
+  const int n_in = 2 * D + CB + 2, pitch = (n_in + 3) & ~3;  // k, q, the slice's v, beta, g
   auto issue = [&](int i) {
     float* dst = sm + (size_t)(i % DELTA_RING) * pitch;
     const float* row = prep + (size_t)(r0 + i) * ldp;
@@ -240,8 +244,8 @@ delta_recurrence_quad_kernel(const float* __restrict__ prep, long ldp, DeltaDims
       size_t off;
       if (e < D) off = (size_t)m.Hk * D + (size_t)kh * D + e;                   // k
       else if (e < 2 * D) off = (size_t)kh * D + (e - D);                        // q
-      else if (e < 2 * D + Dv) off = (size_t)m.n_qk() + (size_t)h * Dv + (e - 2 * D);   // v
-      else off = e == 2 * D + Dv ? (size_t)(Nc + h) : (size_t)(Nc + m.H + h);    // beta, g
+      else if (e < 2 * D + CB) off = (size_t)m.n_qk() + (size_t)h * Dv + blockIdx.z * CB + (e - 2 * D);   // v
+      else off = e == 2 * D + CB ? (size_t)(Nc + h) : (size_t)(Nc + m.H + h);    // beta, g
       cp_async4(dst + e, row + off);
     }
   };
@@ -263,7 +267,7 @@ delta_recurrence_quad_kernel(const float* __restrict__ prep, long ldp, DeltaDims
       qq[c] = *reinterpret_cast<const float4*>(in + D + 32 * c + 4 * sub);
     }
     const float4 v = *reinterpret_cast<const float4*>(in + 2 * D + 4 * cg);
-    const float beta = in[2 * D + Dv], g = in[2 * D + Dv + 1];
+    const float beta = in[2 * D + CB], g = in[2 * D + CB + 1];
     float4 sk = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int c = 0; c < NI; ++c) {
@@ -310,7 +314,7 @@ delta_recurrence_quad_kernel(const float* __restrict__ prep, long ldp, DeltaDims
       o4.z += __shfl_xor_sync(0xffffffffu, o4.z, o);
       o4.w += __shfl_xor_sync(0xffffffffu, o4.w, o);
     }
-    if (sub == 0) *reinterpret_cast<float4*>(o_raw + (size_t)(r0 + i) * ldo + (size_t)h * Dv + 4 * cg) = o4;
+    if (sub == 0) *reinterpret_cast<float4*>(o_raw + (size_t)(r0 + i) * ldo + (size_t)h * Dv + col0) = o4;
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
   if (write_state) {
@@ -325,9 +329,10 @@ template <int D>
 int launch_delta_recurrence_quad(const float* prep, long ldp, DeltaDims m, float* state, const int32_t* seq_q_start,
                                  const int32_t* seq_slot, float* o_raw, long ldo, int n_seqs, int write_state,
                                  cudaStream_t stream) {
-  const size_t smem = (size_t)DELTA_RING * ((2 * D + m.Dv + 2 + 3) & ~3) * sizeof(float);
-  return launch_pdl(PDL_ATTENTION, delta_recurrence_quad_kernel<D>, dim3(m.H, n_seqs), dim3(2 * m.Dv), smem, stream, prep, ldp, m,
-                    state, seq_q_start, seq_slot, o_raw, ldo, write_state);
+  const int CB = m.Dv % 32 == 0 ? 32 : 16;                   // columns per block
+  const size_t smem = (size_t)DELTA_RING * ((2 * D + CB + 2 + 3) & ~3) * sizeof(float);
+  return launch_pdl(PDL_ATTENTION, delta_recurrence_quad_kernel<D>, dim3(m.H, n_seqs, m.Dv / CB), dim3(2 * CB), smem, stream, prep,
+                    ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, write_state);
 }
 
 // One warp per (token, head): out = o / sqrt(mean(o^2) + eps) * w * silu(gate).
@@ -377,7 +382,7 @@ int launch_delta_recurrence(const float* prep, long ldp, DeltaDims m, float* sta
 using namespace llmi;
 
 static int delta_dims_ok(const DeltaDims& m) {
-  return m.H > 0 && m.Hk > 0 && m.D > 0 && m.Dv > 0 && m.taps >= 1 && m.taps <= DELTA_MAX_TAPS && m.H % m.Hk == 0 && m.Dv <= 256;
+  return m.H > 0 && m.Hk > 0 && m.D > 0 && m.Dv > 0 && m.taps >= 1 && m.taps <= DELTA_MAX_TAPS && m.H % m.Hk == 0 && m.Dv <= 1024;
 }
 
 LLMI_EXPORT long llmi_delta_state_floats(int H, int Hk, int D, int Dv, int taps) {
@@ -391,7 +396,13 @@ LLMI_EXPORT int llmi_delta_prepare(const float* proj, long ld, int H, int Hk, in
   const DeltaDims m{H, Hk, D, Dv, taps};
   if (n_tokens <= 0 || !delta_dims_ok(m)) return LLMI_ERR_BAD_SIZE;
   const size_t smem = (size_t)m.n_qk() * sizeof(float);
-  if (smem > 48 * 1024) return LLMI_ERR_BAD_SIZE;
+  if (smem > 200 * 1024) return LLMI_ERR_BAD_SIZE;
+  static PerDevice<size_t> allowed;
+  if (smem > 48 * 1024 && allowed.here() < smem) {
+    if (cudaFuncSetAttribute(delta_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return LLMI_ERR_BAD_SIZE;
+    allowed.here() = smem;
+  }
   // a handful of tokens: many threads a token, so that the few blocks' loads overlap; a prompt: many blocks already
   const int threads = n_tokens <= 64 ? 512 : 128;
   return launch_pdl(PDL_SMALL, delta_prepare_kernel, n_tokens, threads, smem, stream, proj, ld, m, conv_w, a_log, dt_bias, state,
@@ -414,7 +425,7 @@ LLMI_EXPORT int llmi_delta_recurrence(const float* prep, long ldp, int H, int Hk
   const DeltaDims m{H, Hk, D, Dv, taps};
   if (n_seqs <= 0 || n_seqs > 65535 || !delta_dims_ok(m)) return LLMI_ERR_BAD_SIZE;
   // (16-byte accesses: state rows, o rows and the ring's v entries must be 16-byte aligned)
-  if (Dv <= 128 && Dv % 16 == 0 && ldo % 4 == 0 && !((uintptr_t)state & 15) && !((uintptr_t)o_raw & 15) &&
+  if (Dv % 16 == 0 && ldo % 4 == 0 && !((uintptr_t)state & 15) && !((uintptr_t)o_raw & 15) &&
       DeltaDims{H, Hk, D, Dv, taps}.state_floats() % 4 == 0) {
     if (D == 32) return launch_delta_recurrence_quad<32>(prep, ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, n_seqs, write_state, stream);
     if (D == 64) return launch_delta_recurrence_quad<64>(prep, ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, n_seqs, write_state, stream);

@@ -62,6 +62,7 @@ struct SkinnyParams {
   const float* in_ss;         // [in_tiles, SK_SS_STRIDE] as written by the product before
   int in_tiles;
   float in_eps;
+  int act;                    // the gate's activation in mode SK_SWIGLU (see gated_value)
 };
 
 // One copy fetches [4 k slices][rows][64 k]: the matrix is seen as a 3-D tensor (k within a slice, row, slice).
@@ -245,7 +246,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           gu[h] = v * sc;
         }
         ((__nv_bfloat16*)p.out)[(size_t)tok * p.ldo + (m0 >> 1) + f] =
-            __float2bfloat16_rn(__fdividef(gu[0], 1.0f + __expf(-gu[0])) * gu[1]);
+            __float2bfloat16_rn(gated_value(gu[0], gu[1], p.act));
       }
     } else {
       // NPAD * 16 is a multiple of the 128 consumer threads: every thread makes the same number of rounds, and
@@ -348,7 +349,9 @@ LLMI_EXPORT int llmi_gemm_skinny(const void* x, long ldx, const void* w, long ld
                                  float* emit_ss, const float* in_ss, int in_tiles, float in_eps, int* error_flag,
                                  cudaStream_t stream) {
   if (n_tok <= 0 || n_tok > 64 || m_out <= 0 || k <= 0) return LLMI_ERR_BAD_SIZE;
-  if (mode < 0 || mode > 3) return LLMI_ERR_UNSUPPORTED;
+  if (mode < 0 || mode > OUT_GEGLU_REQUEST) return LLMI_ERR_UNSUPPORTED;
+  const int act = mode == OUT_GEGLU_REQUEST ? 1 : 0;
+  if (mode == OUT_GEGLU_REQUEST) mode = SK_SWIGLU;
   if (mode == SK_SWIGLU && ((m_out & 1) || bias)) return LLMI_ERR_UNSUPPORTED;
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || (ldx & 7) || (ldw & 7)) return LLMI_ERR_ALIGN;
   if (k % 64) return LLMI_ERR_UNSUPPORTED;   // the 3-D view of the matrices needs whole 64-wide k slices
@@ -361,7 +364,7 @@ LLMI_EXPORT int llmi_gemm_skinny(const void* x, long ldx, const void* w, long ld
   rc = sk_make_map(&mx, x, n_tok, k, ldx, n_tok);
   if (rc != LLMI_OK) return rc;
   SkinnyParams p{m_out, n_tok, k, y, ldy, bias, mode, error_flag, n_tok, emit_w, (__nv_bfloat16*)emit_h, emit_ldh, emit_ss,
-                 in_ss, in_tiles, in_eps};
+                 in_ss, in_tiles, in_eps, act};
   const int m_tiles = (m_out + SK_ROWS - 1) / SK_ROWS;
   if (nt == 1) return launch_skinny<1>(mw, mx, p, m_tiles, stream);
   if (nt == 2) return launch_skinny<2>(mw, mx, p, m_tiles, stream);

@@ -470,7 +470,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             }
             __nv_bfloat16* o = (__nv_bfloat16*)bufp + (is_gate ? 0 : 8) * (TC_BM / 2) + (row_in_cta >> 1);
 #pragma unroll
-            for (int c = 0; c < 8; ++c) o[c * (TC_BM / 2)] = __float2bfloat16_rn(__fdividef(g[c], 1.0f + __expf(-g[c])) * u[c]);
+            for (int c = 0; c < 8; ++c) o[c * (TC_BM / 2)] = __float2bfloat16_rn(gated_value(g[c], u[c], p.act));
           } else if (p.mode == OUT_STORE) {
             __nv_bfloat16* o = (__nv_bfloat16*)bufp + row_in_cta;
 #pragma unroll
@@ -706,7 +706,7 @@ __device__ __forceinline__ void wide_way_out(const TcParams& p, const CUtensorMa
     for (int c = 0; c < CPT; ++c) up[c] = __shfl_down_sync(0xffffffffu, v[c], 1);
     if (!(row & 1)) {
 #pragma unroll
-      for (int c = 0; c < CPT; ++c) o[c * (RP / 2)] = __float2bfloat16_rn(__fdividef(v[c], 1.0f + __expf(-v[c])) * up[c]);
+      for (int c = 0; c < CPT; ++c) o[c * (RP / 2)] = __float2bfloat16_rn(gated_value(v[c], up[c], p.act));
     }
   } else {
     const float b = (p.bias && m < p.m_out) ? p.bias[m] : 0.f;
@@ -1097,7 +1097,9 @@ LLMI_EXPORT int llmi_gemm_tc(const void* x, long ldx, const void* w, long ldw, c
                              int n_tok, int m_out, int k, int mode, float* workspace, long workspace_bytes,
                              int* tickets, int n_tickets, int* error_flag, cudaStream_t stream) {
   if (n_tok <= 0 || m_out <= 0 || k <= 0) return LLMI_ERR_BAD_SIZE;
-  if (mode < 0 || mode > 3) return LLMI_ERR_UNSUPPORTED;
+  if (mode < 0 || mode > OUT_GEGLU_REQUEST) return LLMI_ERR_UNSUPPORTED;
+  const int act = mode == OUT_GEGLU_REQUEST ? 1 : 0;
+  if (mode == OUT_GEGLU_REQUEST) mode = OUT_SWIGLU;
   if (mode == OUT_SWIGLU && ((m_out & 1) || bias)) return LLMI_ERR_UNSUPPORTED;
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || (ldx & 7) || (ldw & 7)) return LLMI_ERR_ALIGN;
   const int bn = tc_bn(n_tok, m_out);
@@ -1114,7 +1116,7 @@ LLMI_EXPORT int llmi_gemm_tc(const void* x, long ldx, const void* w, long ldw, c
     if (rc != LLMI_OK) return rc;
     rc = boxed3d ? make_map_3d(&mx, x, n_tok, k, ldx, bn, 2) : make_map(&mx, x, n_tok, k, ldx, bn);
     if (rc != LLMI_OK) return rc;
-    TcParams pk{m_out, n_tok, k, y, ldy, bias, mode, 1, nullptr, nullptr, error_flag};
+    TcParams pk{m_out, n_tok, k, y, ldy, bias, mode, 1, nullptr, nullptr, error_flag, act};
     const int m_tiles = (m_out + TC_BM - 1) / TC_BM, n_tiles = (n_tok + bn - 1) / bn;
     // the way out by TMA: a CTA of a cluster of W stores [bn tokens][128 / W rows] (gated: half as many features)
     CUtensorMap mo = mw;
@@ -1149,13 +1151,13 @@ LLMI_EXPORT int llmi_gemm_tc(const void* x, long ldx, const void* w, long ldw, c
       const int pbn = pair_token_tile(n_tok, m_out);
       rc = make_map(&mx, x, n_tok, k, ldx, pbn / 2);
       if (rc != LLMI_OK) return rc;
-      TcParams pp{m_out, n_tok, k, y, ldy, bias, mode, 1, workspace, tickets, error_flag};
+      TcParams pp{m_out, n_tok, k, y, ldy, bias, mode, 1, workspace, tickets, error_flag, act};
       return launch_tc_pair(mw, mx, mo, pp, (m_out + 255) / 256, (n_tok + pbn - 1) / pbn, pbn, out_rc == LLMI_OK, stream);
     }
   }
   rc = make_map(&mx, x, n_tok, k, ldx, bn);
   if (rc != LLMI_OK) return rc;
-  TcParams p{m_out, n_tok, k, y, ldy, bias, mode, splits, workspace, tickets, error_flag};
+  TcParams p{m_out, n_tok, k, y, ldy, bias, mode, splits, workspace, tickets, error_flag, act};
   const int m_tiles = (m_out + TC_BM - 1) / TC_BM, n_tiles = (n_tok + bn - 1) / bn;
   if ((long)m_tiles * n_tiles * splits > 0x7fffffffL) return LLMI_ERR_BAD_SIZE;
   switch (bn) {

@@ -14,7 +14,6 @@ constexpr int TC_BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
 constexpr int TC_THREADS = 192;
 
 constexpr int OUT_STORE = 0, OUT_STORE_F32 = 1, OUT_ADD_F32 = 2, OUT_SWIGLU = 3;
-
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -68,6 +67,7 @@ struct TcParams {
   float* workspace;         // [splits][tiles][BN][128] fp32 when splits > 1
   int* tickets;             // [tiles], zero before and after the launch
   int* error_flag;
+  int act;                  // the gate's activation in mode OUT_SWIGLU (see gated_value)
 };
 
 // The epilogue of one thread: v holds 16 consecutive tokens (n_base..) of out feature m.  Called by all
@@ -87,7 +87,7 @@ __device__ __forceinline__ void tc_epilogue_store(const TcParams& p, float* v, i
       const float g = is_gate ? v[c] : recv, u = is_gate ? recv : v[c + 8];
       const int tok = is_gate ? c : c + 8;
       if (tok < n_valid && m < p.m_out)
-        o[(size_t)tok * p.ldo] = __float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-g)) * u);   // bf16 result: fast exp and divide suffice
+        o[(size_t)tok * p.ldo] = __float2bfloat16_rn(gated_value(g, u, p.act));
     }
     return;
   }

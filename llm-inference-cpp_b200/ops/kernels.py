@@ -20,6 +20,8 @@ OUT_STORE = 0        # y (compute type) = x·Wᵀ
 OUT_STORE_F32 = 1    # y (fp32) = x·Wᵀ
 OUT_ADD_F32 = 2      # y (fp32) += x·Wᵀ
 OUT_SWIGLU = 3       # y (compute type) = silu(gate)·up, W's rows alternating gate and up rows (tensor-core kernel only)
+OUT_GEGLU = 4        # the same with the tanh form of GELU as the gate's activation
+_GATED = (OUT_SWIGLU, OUT_GEGLU)
 
 _ERRORS = {
     -1: "unsupported element type",
@@ -194,7 +196,7 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float
 
 ACT_SILU, ACT_GELU_TANH = 0, 1
 ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH}
-FUSED_GATE_MODES = {ACT_SILU: OUT_SWIGLU}     # activation -> the output mode of the products that gate in their epilogue
+FUSED_GATE_MODES = {ACT_SILU: OUT_SWIGLU, ACT_GELU_TANH: OUT_GEGLU}     # activation -> the output mode of the products that gate in their epilogue
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, act: int = ACT_SILU) -> None:
@@ -280,9 +282,9 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Ten
     _need_cuda(x, w, out, bias)
     M, K = x.shape
     N = w.shape[0]
-    assert w.shape[1] == K and out.shape == (M, N // 2 if mode == OUT_SWIGLU else N)
+    assert w.shape[1] == K and out.shape == (M, N // 2 if mode in _GATED else N)
     assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
-    assert out.dtype == (torch.bfloat16 if mode in (OUT_STORE, OUT_SWIGLU) else torch.float32)
+    assert out.dtype == (torch.bfloat16 if mode in (OUT_STORE, *_GATED) else torch.float32)
     if bias is not None:
         assert bias.dtype == torch.float32 and bias.numel() == N
     sc = tc_scratch(x.device)
@@ -327,9 +329,9 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch
     _need_cuda(x, w, out, bias)
     M, K = x.shape
     N = w.shape[0]
-    assert w.shape[1] == K and out.shape == (M, N // 2 if mode == OUT_SWIGLU else N)
+    assert w.shape[1] == K and out.shape == (M, N // 2 if mode in _GATED else N)
     assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
-    assert out.dtype == (torch.bfloat16 if mode in (OUT_STORE, OUT_SWIGLU) else torch.float32)
+    assert out.dtype == (torch.bfloat16 if mode in (OUT_STORE, *_GATED) else torch.float32)
     if bias is not None:
         assert bias.dtype == torch.float32 and bias.numel() == N
     if then_norm is not None:

@@ -76,3 +76,14 @@ def test_oracle_experts_weights_sum_to_one_over_the_chosen():
     logits = np.array([[1.0, 3.0, 3.0, -1.0], [0.0, 0.0, 0.0, 0.0]])
     idx, wt = G.choose_experts(logits, 2)
     assert idx.tolist() == [[1, 2], [0, 1]] and np.allclose(wt, 0.5)
+
+
+def test_random_model_folder_of_the_design(tmp_path):
+    """The library's seeded random folders work for this design as for any registered one; the plain reader takes them."""
+    import torch
+    from llmi_b200 import write_random_model
+    d = write_random_model(str(tmp_path / "m"), M.LOOPED, 3, torch.bfloat16)
+    cfg, w = G.read_model(d)
+    assert cfg == M.LOOPED and w["loop.step"].shape == (3, 48) and w["l1.norm1.alpha"].shape == ()
+    logits = G.forward(cfg, w, [1, 2, 3, 4])
+    assert logits.shape == (4, 101) and np.isfinite(logits).all()

@@ -47,6 +47,7 @@ def loaded(tmp_path_factory):
 def check(got, refs, dtype):
     assert set(got) == set(refs)
     bad = total = 0
+    errs = []
     for r in refs:
         assert got[r].shape == refs[r].shape
         assert np.isfinite(got[r]).all(), f"{r}: non-finite logits (something outside the sequence or its state was read)"
@@ -57,8 +58,12 @@ def check(got, refs, dtype):
         else:
             bad += int((err > TOL16).sum())
             total += len(err)
+            errs.extend(err.tolist())
     if dtype != "float32":
-        assert bad <= max(1, 0.04 * total), (bad, total)
+        # a router that decides a close call the other way changes that token's row, and through state and attention
+        # the rows behind it: a tenth of the rows may be off, the typical row must be well inside
+        assert bad <= max(1, 0.10 * total), (bad, total)
+        assert float(np.median(errs)) < TOL16 / 3, float(np.median(errs))
 
 
 ALL = list(M.CONFIGS)
@@ -141,6 +146,35 @@ def test_greedy_generation_through_the_entry_point(loaded, name):
     ref = [G.generate_greedy(cfg, w, p, n) for p, n in zip(prompts, new)]
     assert out == ref
     assert L.generate(model, prompts, max_new=new, max_batch=3, use_graphs=False) == ref
+
+
+def test_programs_as_a_user_calls_them(loaded, tmp_path):
+    """bin/llmi-generate and bin/trace_run on a Garodra folder, as subprocesses: the design is chosen by config.json."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from conftest import ROOT
+    cfg = M.CONFIGS["looped"]
+    d = str(tmp_path / "model")
+    w = M.write_model(d, cfg, M.make_weights(cfg, 7), "F32")
+    prompt = [3, 17, 90, 4, 4, 56]
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "llmi-generate"), d, "--ids", ",".join(map(str, prompt)),
+                        "--max-new", "6", "--json", "--dtype", "fp32"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert json.loads(r.stdout.strip().splitlines()[-1])["generated_ids"] == G.generate_greedy(cfg, w, prompt, 6)
+    reqs = requests_for(cfg, [5, 70, 33])
+    steps, most = H.trace_batches(reqs, 3, {"r0": 2, "r1": 40, "r2": 33})
+    out = tmp_path / "out"
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype", "float32",
+                        "--out", str(out), "--max-tokens", str(most)],
+                       input="".join(json.dumps(s_) + "\n" for s_ in steps), capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    outs = []
+    for s_ in steps:
+        n = sum(len(e["want"]) for e in s_["entries"])
+        outs.append(np.fromfile(out / f"{s_['step']}.f32", dtype="<f4").reshape(n, -1) if n else None)
+    check(H.collect(steps, outs, cfg["vocab"]), {r: G.forward(cfg, w, t) for r, t in reqs.items()}, "float32")
 
 
 # ----------------------------------------------------------------------------- kernels alone
@@ -265,6 +299,29 @@ def test_grouped_experts_equal_streamed_experts(T, E, top, W, F):
     kernels.moe_experts_grouped(h, wg, wu, wd, idx, wt, kernels.ACT_SILU, rt, y_g)
     assert torch.isfinite(y_g).all() and (y_g[7] == 0).all()
     assert float((y_g - y_s).abs().max()) < 2e-2 * max(1.0, float(y_s.abs().max()))
+
+
+@pytest.mark.parametrize("T", [3, 16, 40, 300, 700])
+def test_gelu_gate_fused_into_the_product_equals_the_two_step_form(T):
+    """act(gate) * up finished in the product's epilogue (weight rows alternating gate and up) against the product
+    followed by the gating kernel, for the weight-streaming and the tcgen05 kernels' ranges of tokens."""
+    import torch
+    from llmi_b200.ops import kernels
+    gen = torch.Generator(device="cuda:0").manual_seed(T)
+    W, F = 128, 192
+    h = (torch.randn(T, W, generator=gen, device="cuda:0") * 1.5).to(torch.bfloat16)
+    gate = (torch.randn(F, W, generator=gen, device="cuda:0") * W ** -0.5).to(torch.bfloat16)
+    up = (torch.randn(F, W, generator=gen, device="cuda:0") * W ** -0.5).to(torch.bfloat16)
+    fused = torch.empty(T, F, dtype=torch.bfloat16, device="cuda:0")
+    kernels.gemm_bf16(h, torch.stack([gate, up], dim=1).reshape(2 * F, W).contiguous(), fused, None, kernels.OUT_GEGLU)
+    gu = torch.empty(T, 2 * F, dtype=torch.bfloat16, device="cuda:0")
+    kernels.linear(h, torch.cat([gate, up]).contiguous(), gu)
+    two = torch.empty(T, F, dtype=torch.bfloat16, device="cuda:0")
+    kernels.swiglu(gu, two, kernels.ACT_GELU_TANH)
+    g64, u64 = h.double() @ gate.double().T, h.double() @ up.double().T
+    ref = 0.5 * g64 * (1 + torch.tanh(0.7978845608028654 * (g64 + 0.044715 * g64 ** 3))) * u64
+    scale = float(ref.abs().max())                                # results are rounded to bf16: 2^-9 of their size, twice in two steps
+    assert float((fused.double() - ref).abs().max()) < 6e-3 * scale and float((two.double() - ref).abs().max()) < 2e-2 * scale
 
 
 def test_the_oracle_itself_the_folded_form_of_latent_attention():
