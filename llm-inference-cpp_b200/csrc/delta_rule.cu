@@ -3,7 +3,8 @@
 // with q, k unit vectors (q also times D^-1/2), a decay g in (0, 1) and a write strength beta in (0, 1).
 // q, k, v first pass a short causal convolution over time (per channel, no bias) and silu.  The state of a
 // sequence is S (fp32) and the last taps-1 inputs of the convolution (fp32); both live in the cache's state slab,
-// one row per slot:  [ S: H*D*Dv | conv: (taps-1) * Nc ],  Nc = 2*Hk*D + H*Dv channels.
+// one row per slot:  [ S: H*Dv*D | conv: (taps-1) * Nc ],  Nc = 2*Hk*D + H*Dv channels.  S is kept column by column
+// ([head][column j][entry d]): the threads that share a column read and write neighbouring words.
 //
 // Everything here is fp32 arithmetic.  Kernels, in the order of a step:
 //   llmi_delta_prepare      per token: convolution + silu, unit norms, beta, decay          (parallel over tokens)
@@ -32,17 +33,33 @@ struct DeltaDims {
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
-// One block per token.  prep: fp32 [T, Nc + 2H]: [ q^ | k^ | v (after convolution and silu) | beta | decay ].
-__global__ void __launch_bounds__(512)
+// One block per (token, piece).  Pieces 0 .. 2 Hk - 1: one head of q or k (convolution, silu, unit norm); the pieces
+// behind them: 256 channels of v each (convolution, silu); the last piece also makes beta and decay of every head.
+// prep: fp32 [T, Nc + 2H]: [ q^ | k^ | v | beta | decay ].
+constexpr int DELTA_V_PIECE = 256;
+
+__device__ __forceinline__ float delta_conv_one(const float* __restrict__ proj, long ld, const float* __restrict__ carry,
+                                                const float* __restrict__ conv_w, int ch, int Nc, int K, int pos, int p0, int r0) {
+  float acc = 0.f;
+  for (int d = K - 1; d >= 0; --d) {                     // oldest tap first
+    const int p = pos - d;
+    if (p < 0) continue;
+    const float x = p >= p0 ? proj[(size_t)(r0 + (p - p0)) * ld + ch] : carry[(size_t)(p - (p0 - (K - 1))) * Nc + ch];
+    acc = fmaf(x, conv_w[(size_t)ch * K + (K - 1 - d)], acc);
+  }
+  return silu_f(acc);
+}
+
+__global__ void __launch_bounds__(256)
 delta_prepare_kernel(const float* __restrict__ proj, long ld, DeltaDims m, const float* __restrict__ conv_w,
                      const float* __restrict__ a_log, const float* __restrict__ dt_bias, const float* __restrict__ state,
                      const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ tok_pos,
                      const int32_t* __restrict__ seq_q_start, const int32_t* __restrict__ seq_slot,
                      float* __restrict__ prep, long ldp) {
-  extern __shared__ float qk_s[];                        // [2*Hk*D] convolved q and k of this token
+  __shared__ float scratch[32];
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x;
+  const int t = blockIdx.x, piece = blockIdx.y;
   const int seq = tok_seq[t];
   if (seq < 0) return;
   const int slot = seq_slot[seq];
@@ -52,33 +69,31 @@ delta_prepare_kernel(const float* __restrict__ proj, long ld, DeltaDims m, const
   const int K = m.taps, Nc = m.n_conv(), Nqk = m.n_qk();
   const float* carry = state + (size_t)slot * m.state_floats() + m.conv_offset();   // [K-1][Nc]: positions p0-(K-1) .. p0-1
   float* out = prep + (size_t)t * ldp;
-  for (int ch = threadIdx.x; ch < Nc; ch += blockDim.x) {
-    float acc = 0.f;
-    for (int d = K - 1; d >= 0; --d) {                   // oldest tap first
-      const int p = pos - d;
-      if (p < 0) continue;
-      const float x = p >= p0 ? proj[(size_t)(r0 + (p - p0)) * ld + ch] : carry[(size_t)(p - (p0 - (K - 1))) * Nc + ch];
-      acc = fmaf(x, conv_w[(size_t)ch * K + (K - 1 - d)], acc);
-    }
-    const float y = silu_f(acc);
-    if (ch < Nqk) qk_s[ch] = y; else out[ch] = y;
-  }
-  __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
-  for (int hh = warp; hh < 2 * m.Hk; hh += nwarp) {      // heads of q, then heads of k
-    const float* src = qk_s + (size_t)hh * m.D;
+  if (piece < 2 * m.Hk) {
+    // a head of q (pieces 0 .. Hk-1) or of k: its D channels, then the unit norm over them
+    const int base = piece * m.D;
     float ss = 0.f;
-    for (int d = lane; d < m.D; d += 32) ss = fmaf(src[d], src[d], ss);
-    ss = warp_sum(ss);
+    for (int d = threadIdx.x; d < m.D; d += blockDim.x) {
+      const float y = delta_conv_one(proj, ld, carry, conv_w, base + d, Nc, K, pos, p0, r0);
+      out[base + d] = y;                                 // (kept here until the scale is known; the same thread comes back)
+      ss = fmaf(y, y, ss);
+    }
+    ss = block_sum(ss, scratch);
     float sc = 1.0f / sqrtf(ss + 1e-6f);
-    if (hh < m.Hk) sc *= 1.0f / sqrtf((float)m.D);
-    for (int d = lane; d < m.D; d += 32) out[(size_t)hh * m.D + d] = src[d] * sc;
+    if (piece < m.Hk) sc *= 1.0f / sqrtf((float)m.D);
+    for (int d = threadIdx.x; d < m.D; d += blockDim.x) out[base + d] *= sc;
+    return;
   }
-  const float* row = proj + (size_t)t * ld;
-  for (int h = threadIdx.x; h < m.H; h += blockDim.x) {
-    const float b = row[Nc + h], a = row[Nc + m.H + h];
-    out[Nc + h] = 1.0f / (1.0f + expf(-b));
-    out[Nc + m.H + h] = expf(-expf(a_log[h]) * softplus_f(a + dt_bias[h]));
+  const int vp = piece - 2 * m.Hk, n_v = m.H * m.Dv;
+  for (int c = vp * DELTA_V_PIECE + threadIdx.x; c < min(n_v, (vp + 1) * DELTA_V_PIECE); c += blockDim.x)
+    out[Nqk + c] = delta_conv_one(proj, ld, carry, conv_w, Nqk + c, Nc, K, pos, p0, r0);
+  if (piece == (int)gridDim.y - 1) {
+    const float* row = proj + (size_t)t * ld;
+    for (int h = threadIdx.x; h < m.H; h += blockDim.x) {
+      const float b = row[Nc + h], a = row[Nc + m.H + h];
+      out[Nc + h] = 1.0f / (1.0f + expf(-b));
+      out[Nc + m.H + h] = expf(-expf(a_log[h]) * softplus_f(a + dt_bias[h]));
+    }
   }
 }
 
@@ -136,9 +151,9 @@ delta_recurrence_kernel(const float* __restrict__ prep, long ldp, DeltaDims m, f
   if (live) {
     if (DREG > 0) {
 #pragma unroll
-      for (int d = 0; d < DREG; ++d) S_r[d] = S_g[(size_t)d * Dv + j];
+      for (int d = 0; d < DREG; ++d) S_r[d] = S_g[(size_t)j * D + d];
     } else {
-      for (int d = 0; d < D; ++d) S_s[(size_t)d * cols + j] = S_g[(size_t)d * Dv + j];
+      for (int d = 0; d < D; ++d) S_s[(size_t)d * cols + j] = S_g[(size_t)j * D + d];
     }
   }
   const int Nc = m.n_conv();
@@ -185,23 +200,22 @@ delta_recurrence_kernel(const float* __restrict__ prep, long ldp, DeltaDims m, f
   if (live && write_state) {
     if (DREG > 0) {
 #pragma unroll
-      for (int d = 0; d < DREG; ++d) S_g[(size_t)d * Dv + j] = S_r[d];
+      for (int d = 0; d < DREG; ++d) S_g[(size_t)j * D + d] = S_r[d];
     } else {
-      for (int d = 0; d < D; ++d) S_g[(size_t)d * Dv + j] = S_s[(size_t)d * cols + j];
+      for (int d = 0; d < D; ++d) S_g[(size_t)j * D + d] = S_s[(size_t)d * cols + j];
     }
   }
 }
 
-// The form for D = 32, 64, 128 and Dv a multiple of 16.  A thread holds FOUR neighbouring columns of S and an eighth of
-// their entries (lane `sub` of eight: d = 32 i + 4 sub + 0..3), in registers.  Every thread reads k and q from shared
-// memory, so the reads of a token are 2 D Dv / (columns per thread) floats: four columns per thread is what brings
-// them below the token's arithmetic (3 D Dv multiply-adds).  Partial sums over d are joined by three shuffles.
-// The recurrence is a chain over the tokens: the time of a prompt is tokens x (time of one token).  Columns are
-// independent, so a head's columns are cut into slices of 32 (or 16) and every slice is a block of its own
-// (blockIdx.z): more SMs at work on one prompt, and fewer instructions per token on each.
+// The form for D = 32, 64, 128 and Dv a multiple of 16.  A thread holds TWO neighbouring columns of S and a
+// sixteenth of their entries (lane `sub` of sixteen: d = 64 i + 4 sub + 0..3, while d < D), in registers; partial sums
+// over d are joined by four shuffles.  The recurrence is a chain over the tokens — the time of a prompt is tokens x
+// (time of one token), and a token costs one warp's instructions (each warp has a scheduler to itself) — so the
+// work of a token is spread thin: 16 columns a warp.  Columns are independent: a head's columns are cut into slices
+// of 32 (or 16) and every slice is a block of its own (blockIdx.z).
 //
-// What a token needs — k, q of the head's key head, v of the head, beta, g: 2*D + Dv + 2 floats — is copied into a ring
-// of DELTA_RING entries DELTA_RING - 1 tokens ahead (cp.async, no registers in between), so that no load's latency
+// What a token needs — k, q of the head's key head, the slice's v, beta, g — is copied into a ring of DELTA_RING
+// entries DELTA_RING - 1 tokens ahead (cp.async, 16 bytes a copy, no registers in between), so that no load's latency
 // lies on the chain from token to token; one barrier per token.
 constexpr int DELTA_RING = 8;
 
@@ -209,9 +223,13 @@ __device__ __forceinline__ void cp_async4(void* dst, const void* src) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
 }
+__device__ __forceinline__ void cp_async16_ca(void* dst, const void* src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
 
 template <int D>
-__global__ void __launch_bounds__(64)
+__global__ void __launch_bounds__(256)
 delta_recurrence_quad_kernel(const float* __restrict__ prep, long ldp, DeltaDims m, float* __restrict__ state,
                              const int32_t* __restrict__ seq_q_start, const int32_t* __restrict__ seq_slot,
                              float* __restrict__ o_raw, long ldo, int write_state) {
@@ -223,30 +241,38 @@ delta_recurrence_quad_kernel(const float* __restrict__ prep, long ldp, DeltaDims
   if (slot < 0) return;
   const int r0 = seq_q_start[seq], n = seq_q_start[seq + 1] - r0;
   if (n <= 0) return;
-  constexpr int NI = D / 32;                                 // chunks of four entries per lane
+  constexpr int NI = (D + 63) / 64;                          // chunks of four entries per lane (D = 32: lanes 8..15 hold none)
   const int Dv = m.Dv;
-  const int CB = blockDim.x >> 1;                            // columns of this block's slice (the launcher gives 2 CB threads)
-  const int cg = threadIdx.x >> 3, sub = threadIdx.x & 7;    // my columns: col0 .. col0 + 3
-  const int col0 = blockIdx.z * CB + 4 * cg;
+  const int CB = blockDim.x >> 3;                            // columns of this block's slice (the launcher gives 8 CB threads)
+  const int cg = threadIdx.x >> 4, sub = threadIdx.x & 15;   // my columns: col0, col0 + 1
+  const int col0 = blockIdx.z * CB + 2 * cg;
+  const bool holds = 4 * sub < D;                            // (D = 32 only: half of the lanes carry zeros)
   const int kh = h / (m.H / m.Hk);
-  float* S_g = state + (size_t)slot * m.state_floats() + (size_t)h * D * Dv + col0;
-  float4 S_r[NI][4];                                         // [chunk][entry of the chunk] . (x, y, z, w) = the four columns
+  float* S_g = state + (size_t)slot * m.state_floats() + (size_t)h * D * Dv + (size_t)col0 * D;    // [column][entry]
+  float2 S_r[NI][4];                                         // [chunk][entry of the chunk] . (x, y) = the two columns
 #pragma unroll
-  for (int i = 0; i < NI; ++i)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) S_r[i][e] = *reinterpret_cast<const float4*>(S_g + (size_t)(32 * i + 4 * sub + e) * Dv);
+  for (int i = 0; i < NI; ++i) {
+    const float4 c0 = holds ? *reinterpret_cast<const float4*>(S_g + 64 * i + 4 * sub) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 c1 = holds ? *reinterpret_cast<const float4*>(S_g + D + 64 * i + 4 * sub) : make_float4(0.f, 0.f, 0.f, 0.f);
+    S_r[i][0] = make_float2(c0.x, c1.x);
+    S_r[i][1] = make_float2(c0.y, c1.y);
+    S_r[i][2] = make_float2(c0.z, c1.z);
+    S_r[i][3] = make_float2(c0.w, c1.w);
+  }
   const int Nc = m.n_conv();
-  const int n_in = 2 * D + CB + 2, pitch = (n_in + 3) & ~3;  // k, q, the slice's v, beta, g
+  // ring entry: [k (D) | q (D) | v of the slice (CB) | beta, g, 0, 0]; all parts are whole 16-byte pieces
+  const int n16 = (2 * D + CB) / 4, pitch = 2 * D + CB + 4;
+  const float* k_src = prep + (size_t)m.Hk * D + (size_t)kh * D;
+  const float* q_src = prep + (size_t)kh * D;
+  const float* v_src = prep + (size_t)m.n_qk() + (size_t)h * Dv + blockIdx.z * CB;
   auto issue = [&](int i) {
     float* dst = sm + (size_t)(i % DELTA_RING) * pitch;
-    const float* row = prep + (size_t)(r0 + i) * ldp;
-    for (int e = threadIdx.x; e < n_in; e += blockDim.x) {
-      size_t off;
-      if (e < D) off = (size_t)m.Hk * D + (size_t)kh * D + e;                   // k
-      else if (e < 2 * D) off = (size_t)kh * D + (e - D);                        // q
-      else if (e < 2 * D + CB) off = (size_t)m.n_qk() + (size_t)h * Dv + blockIdx.z * CB + (e - 2 * D);   // v
-      else off = e == 2 * D + CB ? (size_t)(Nc + h) : (size_t)(Nc + m.H + h);    // beta, g
-      cp_async4(dst + e, row + off);
+    const size_t row = (size_t)(r0 + i) * ldp;
+    for (int e = threadIdx.x; e < n16 + 2; e += blockDim.x) {
+      if (e < D / 4) cp_async16_ca(dst + 4 * e, k_src + row + 4 * e);
+      else if (e < D / 2) cp_async16_ca(dst + 4 * e, q_src + row + 4 * (e - D / 4));
+      else if (e < n16) cp_async16_ca(dst + 4 * e, v_src + row + 4 * (e - D / 2));
+      else cp_async4(dst + 4 * n16 + (e - n16), prep + row + (e == n16 ? Nc + h : Nc + m.H + h));
     }
   };
 #pragma unroll
@@ -263,65 +289,67 @@ delta_recurrence_quad_kernel(const float* __restrict__ prep, long ldp, DeltaDims
     float4 kk[NI], qq[NI];
 #pragma unroll
     for (int c = 0; c < NI; ++c) {
-      kk[c] = *reinterpret_cast<const float4*>(in + 32 * c + 4 * sub);
-      qq[c] = *reinterpret_cast<const float4*>(in + D + 32 * c + 4 * sub);
+      kk[c] = holds ? *reinterpret_cast<const float4*>(in + 64 * c + 4 * sub) : make_float4(0.f, 0.f, 0.f, 0.f);
+      qq[c] = holds ? *reinterpret_cast<const float4*>(in + D + 64 * c + 4 * sub) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    const float4 v = *reinterpret_cast<const float4*>(in + 2 * D + 4 * cg);
+    const float2 v = *reinterpret_cast<const float2*>(in + 2 * D + 2 * cg);
     const float beta = in[2 * D + CB], g = in[2 * D + CB + 1];
-    float4 sk = make_float4(0.f, 0.f, 0.f, 0.f);
+    float2 sk = make_float2(0.f, 0.f), sk2 = make_float2(0.f, 0.f);
 #pragma unroll
     for (int c = 0; c < NI; ++c) {
-      const float ke[4] = {kk[c].x, kk[c].y, kk[c].z, kk[c].w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        sk.x = fmaf(S_r[c][e].x, ke[e], sk.x);
-        sk.y = fmaf(S_r[c][e].y, ke[e], sk.y);
-        sk.z = fmaf(S_r[c][e].z, ke[e], sk.z);
-        sk.w = fmaf(S_r[c][e].w, ke[e], sk.w);
-      }
+      sk.x = fmaf(S_r[c][0].x, kk[c].x, sk.x);
+      sk.y = fmaf(S_r[c][0].y, kk[c].x, sk.y);
+      sk2.x = fmaf(S_r[c][1].x, kk[c].y, sk2.x);
+      sk2.y = fmaf(S_r[c][1].y, kk[c].y, sk2.y);
+      sk.x = fmaf(S_r[c][2].x, kk[c].z, sk.x);
+      sk.y = fmaf(S_r[c][2].y, kk[c].z, sk.y);
+      sk2.x = fmaf(S_r[c][3].x, kk[c].w, sk2.x);
+      sk2.y = fmaf(S_r[c][3].y, kk[c].w, sk2.y);
     }
+    sk.x += sk2.x;
+    sk.y += sk2.y;
 #pragma unroll
-    for (int o = 1; o < 8; o <<= 1) {
+    for (int o = 1; o < 16; o <<= 1) {
       sk.x += __shfl_xor_sync(0xffffffffu, sk.x, o);
       sk.y += __shfl_xor_sync(0xffffffffu, sk.y, o);
-      sk.z += __shfl_xor_sync(0xffffffffu, sk.z, o);
-      sk.w += __shfl_xor_sync(0xffffffffu, sk.w, o);
     }
-    const float4 u = make_float4(beta * (v.x - g * sk.x), beta * (v.y - g * sk.y), beta * (v.z - g * sk.z), beta * (v.w - g * sk.w));
-    float4 o4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float ux = beta * (v.x - g * sk.x), uy = beta * (v.y - g * sk.y);
+    float2 o2 = make_float2(0.f, 0.f), o3 = make_float2(0.f, 0.f);
 #pragma unroll
     for (int c = 0; c < NI; ++c) {
       const float ke[4] = {kk[c].x, kk[c].y, kk[c].z, kk[c].w};
       const float qe[4] = {qq[c].x, qq[c].y, qq[c].z, qq[c].w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        float4 s = S_r[c][e];
-        s.x = fmaf(ke[e], u.x, g * s.x);
-        s.y = fmaf(ke[e], u.y, g * s.y);
-        s.z = fmaf(ke[e], u.z, g * s.z);
-        s.w = fmaf(ke[e], u.w, g * s.w);
+        float2 s = S_r[c][e];
+        s.x = fmaf(ke[e], ux, g * s.x);
+        s.y = fmaf(ke[e], uy, g * s.y);
         S_r[c][e] = s;
-        o4.x = fmaf(s.x, qe[e], o4.x);
-        o4.y = fmaf(s.y, qe[e], o4.y);
-        o4.z = fmaf(s.z, qe[e], o4.z);
-        o4.w = fmaf(s.w, qe[e], o4.w);
+        if (e & 1) {
+          o3.x = fmaf(s.x, qe[e], o3.x);
+          o3.y = fmaf(s.y, qe[e], o3.y);
+        } else {
+          o2.x = fmaf(s.x, qe[e], o2.x);
+          o2.y = fmaf(s.y, qe[e], o2.y);
+        }
       }
     }
+    o2.x += o3.x;
+    o2.y += o3.y;
 #pragma unroll
-    for (int o = 1; o < 8; o <<= 1) {
-      o4.x += __shfl_xor_sync(0xffffffffu, o4.x, o);
-      o4.y += __shfl_xor_sync(0xffffffffu, o4.y, o);
-      o4.z += __shfl_xor_sync(0xffffffffu, o4.z, o);
-      o4.w += __shfl_xor_sync(0xffffffffu, o4.w, o);
+    for (int o = 1; o < 16; o <<= 1) {
+      o2.x += __shfl_xor_sync(0xffffffffu, o2.x, o);
+      o2.y += __shfl_xor_sync(0xffffffffu, o2.y, o);
     }
-    if (sub == 0) *reinterpret_cast<float4*>(o_raw + (size_t)(r0 + i) * ldo + (size_t)h * Dv + col0) = o4;
+    if (sub == 0) *reinterpret_cast<float2*>(o_raw + (size_t)(r0 + i) * ldo + (size_t)h * Dv + col0) = o2;
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
-  if (write_state) {
+  if (write_state && holds) {
 #pragma unroll
-    for (int i = 0; i < NI; ++i)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) *reinterpret_cast<float4*>(S_g + (size_t)(32 * i + 4 * sub + e) * Dv) = S_r[i][e];
+    for (int i = 0; i < NI; ++i) {
+      *reinterpret_cast<float4*>(S_g + 64 * i + 4 * sub) = make_float4(S_r[i][0].x, S_r[i][1].x, S_r[i][2].x, S_r[i][3].x);
+      *reinterpret_cast<float4*>(S_g + D + 64 * i + 4 * sub) = make_float4(S_r[i][0].y, S_r[i][1].y, S_r[i][2].y, S_r[i][3].y);
+    }
   }
 }
 
@@ -330,8 +358,8 @@ int launch_delta_recurrence_quad(const float* prep, long ldp, DeltaDims m, float
                                  const int32_t* seq_slot, float* o_raw, long ldo, int n_seqs, int write_state,
                                  cudaStream_t stream) {
   const int CB = m.Dv % 32 == 0 ? 32 : 16;                   // columns per block
-  const size_t smem = (size_t)DELTA_RING * ((2 * D + CB + 2 + 3) & ~3) * sizeof(float);
-  return launch_pdl(PDL_ATTENTION, delta_recurrence_quad_kernel<D>, dim3(m.H, n_seqs, m.Dv / CB), dim3(2 * CB), smem, stream, prep,
+  const size_t smem = (size_t)DELTA_RING * (2 * D + CB + 4) * sizeof(float);
+  return launch_pdl(PDL_ATTENTION, delta_recurrence_quad_kernel<D>, dim3(m.H, n_seqs, m.Dv / CB), dim3(8 * CB), smem, stream, prep,
                     ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, write_state);
 }
 
@@ -395,18 +423,11 @@ LLMI_EXPORT int llmi_delta_prepare(const float* proj, long ld, int H, int Hk, in
                                    long ldp, int n_tokens, cudaStream_t stream) {
   const DeltaDims m{H, Hk, D, Dv, taps};
   if (n_tokens <= 0 || !delta_dims_ok(m)) return LLMI_ERR_BAD_SIZE;
-  const size_t smem = (size_t)m.n_qk() * sizeof(float);
-  if (smem > 200 * 1024) return LLMI_ERR_BAD_SIZE;
-  static PerDevice<size_t> allowed;
-  if (smem > 48 * 1024 && allowed.here() < smem) {
-    if (cudaFuncSetAttribute(delta_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-      return LLMI_ERR_BAD_SIZE;
-    allowed.here() = smem;
-  }
-  // a handful of tokens: many threads a token, so that the few blocks' loads overlap; a prompt: many blocks already
-  const int threads = n_tokens <= 64 ? 512 : 128;
-  return launch_pdl(PDL_SMALL, delta_prepare_kernel, n_tokens, threads, smem, stream, proj, ld, m, conv_w, a_log, dt_bias, state,
-                    tok_seq, tok_pos, seq_q_start, seq_slot, prep, ldp);
+  const int pieces = 2 * m.Hk + (m.H * m.Dv + DELTA_V_PIECE - 1) / DELTA_V_PIECE;
+  if (pieces > 65535) return LLMI_ERR_BAD_SIZE;
+  const int threads = m.D >= 256 ? 256 : (m.D > 64 ? 128 : 64);
+  return launch_pdl(PDL_SMALL, delta_prepare_kernel, dim3(n_tokens, pieces), dim3(threads), 0, stream, proj, ld, m, conv_w, a_log,
+                    dt_bias, state, tok_seq, tok_pos, seq_q_start, seq_slot, prep, ldp);
 }
 
 LLMI_EXPORT int llmi_delta_conv_carry(const float* proj, long ld, int H, int Hk, int D, int Dv, int taps, float* state,
@@ -425,8 +446,8 @@ LLMI_EXPORT int llmi_delta_recurrence(const float* prep, long ldp, int H, int Hk
   const DeltaDims m{H, Hk, D, Dv, taps};
   if (n_seqs <= 0 || n_seqs > 65535 || !delta_dims_ok(m)) return LLMI_ERR_BAD_SIZE;
   // (16-byte accesses: state rows, o rows and the ring's v entries must be 16-byte aligned)
-  if (Dv % 16 == 0 && ldo % 4 == 0 && !((uintptr_t)state & 15) && !((uintptr_t)o_raw & 15) &&
-      DeltaDims{H, Hk, D, Dv, taps}.state_floats() % 4 == 0) {
+  if (Dv % 16 == 0 && ldo % 4 == 0 && ldp % 4 == 0 && !((uintptr_t)state & 15) && !((uintptr_t)o_raw & 15) &&
+      !((uintptr_t)prep & 15) && DeltaDims{H, Hk, D, Dv, taps}.state_floats() % 4 == 0) {
     if (D == 32) return launch_delta_recurrence_quad<32>(prep, ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, n_seqs, write_state, stream);
     if (D == 64) return launch_delta_recurrence_quad<64>(prep, ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, n_seqs, write_state, stream);
     if (D == 128) return launch_delta_recurrence_quad<128>(prep, ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, n_seqs, write_state, stream);

@@ -33,6 +33,8 @@ struct LatentMmaArgs {
   int n_tokens, n_heads, C, R;
   int heads_per_block, tokens_per_block;    // their product is 16
   int splits, pages_per_split;
+  int page_buffers;             // 2: the next page arrives while the current one is multiplied; 1: half the shared memory,
+                                // so that two blocks share an SM and overlap each other instead (steps of single tokens)
   float scale;
   float* ws_o;                  // [T, H, splits, C]   (splits > 1)
   float* ws_ml;                 // [T, H, splits, 2]
@@ -48,10 +50,11 @@ attention_latent_mma_kernel(const LatentMmaArgs a) {
   pdl_launch_dependents();
   const int Dk = a.C + a.R, ldk = Dk + LM_PAD;               // padded pitch: ldmatrix rows fall on different banks
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(lm_smem);                 // [RG * 16][ldk]
-  __nv_bfloat16* k_s = q_s + RG * LM_ROWS * ldk;                                   // [2][64][ldk]
+  __nv_bfloat16* k_s = q_s + RG * LM_ROWS * ldk;                                   // [page_buffers][64][ldk]
   const int rg = threadIdx.x >> 7;                                                 // my group of 16 rows
-  __nv_bfloat16* p_s = k_s + 2 * LM_KEYS * ldk + rg * LM_ROWS * (LM_KEYS + LM_PAD);         // [RG][16][64 + 8]: my group's
-  float* max_s = reinterpret_cast<float*>(k_s + 2 * LM_KEYS * ldk + RG * LM_ROWS * (LM_KEYS + LM_PAD)) + rg * LM_WARPS * LM_ROWS;   // [RG][4][16]
+  const int nbuf = a.page_buffers;
+  __nv_bfloat16* p_s = k_s + nbuf * LM_KEYS * ldk + rg * LM_ROWS * (LM_KEYS + LM_PAD);      // [RG][16][64 + 8]: my group's
+  float* max_s = reinterpret_cast<float*>(k_s + nbuf * LM_KEYS * ldk + RG * LM_ROWS * (LM_KEYS + LM_PAD)) + rg * LM_WARPS * LM_ROWS;   // [RG][4][16]
   float* sum_s = max_s + RG * LM_WARPS * LM_ROWS;                                  // [RG][4][16]
   const int warp = (threadIdx.x >> 5) & 3, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
   const int t0 = blockIdx.x * a.tokens_per_block, h0 = blockIdx.y * a.heads_per_block, split = blockIdx.z;
@@ -100,10 +103,10 @@ attention_latent_mma_kernel(const LatentMmaArgs a) {
       const int page = a.seq_pages[(size_t)seq * a.pages_stride + pg];
       const __nv_bfloat16* src = a.cache + (size_t)page * LM_KEYS * Dk;
       __nv_bfloat16* dst = k_s + (size_t)buf * LM_KEYS * ldk;
-      for (int idx = threadIdx.x; idx < LM_KEYS * chunks; idx += blockDim.x) {
-        const int r = idx / chunks, c8 = idx - r * chunks;
+      for (int r = threadIdx.x >> 5; r < LM_KEYS; r += RG * LM_WARPS) {          // a warp copies whole rows
         const bool live = page >= 0 && pg * LM_KEYS + r <= newest;
-        cp_async16(dst + r * ldk + 8 * c8, live ? (const void*)(src + (size_t)r * Dk + 8 * c8) : (const void*)a.cache, live ? 16 : 0);
+        const __nv_bfloat16* from = live ? src + (size_t)r * Dk : a.cache;
+        for (int c8 = lane; c8 < chunks; c8 += 32) cp_async16(dst + r * ldk + 8 * c8, live ? from + 8 * c8 : from, live ? 16 : 0);
       }
       cp_async_commit();
     };
@@ -117,10 +120,10 @@ attention_latent_mma_kernel(const LatentMmaArgs a) {
 
     if (pg_lo < pg_hi) fetch(pg_lo, 0);
     for (int pg = pg_lo; pg < pg_hi; ++pg) {
-      const int buf = (pg - pg_lo) & 1;
+      const int buf = nbuf == 2 ? (pg - pg_lo) & 1 : 0;
       cp_async_wait_all();
       __syncthreads();                                         // this page is here; everyone is done with the page before
-      if (pg + 1 < pg_hi) fetch(pg + 1, buf ^ 1);
+      if (nbuf == 2 && pg + 1 < pg_hi) fetch(pg + 1, buf ^ 1);
       const __nv_bfloat16* kt = k_s + (size_t)buf * LM_KEYS * ldk;
 
       // scores of my warp's 16 keys; the k steps go round four sets of accumulators, so that the chain of dependent
@@ -231,6 +234,10 @@ attention_latent_mma_kernel(const LatentMmaArgs a) {
           mma_bf16(o[j], af, bf[0], bf[1]);
           mma_bf16(o[j + 1], af, bf[2], bf[3]);
         }
+      }
+      if (nbuf == 1 && pg + 1 < pg_hi) {
+        __syncthreads();                                       // everyone has read this page out
+        fetch(pg + 1, 0);
       }
     }
     cp_async_wait_all();
@@ -354,12 +361,13 @@ LLMI_EXPORT int llmi_attention_latent_mma(const void* qa, long ldq, void* out, l
   a.n_tokens = n_tokens; a.n_heads = n_heads; a.C = C; a.R = R;
   a.heads_per_block = hpb; a.tokens_per_block = row_groups * LM_ROWS / hpb;
   a.splits = splits; a.pages_per_split = pages_per_split; a.scale = scale;
+  a.page_buffers = row_groups == 1 ? 1 : 2;
   a.ws_o = workspace;
   a.ws_ml = workspace ? workspace + (size_t)n_tokens * n_heads * splits * C : nullptr;
   dim3 grid((n_tokens + a.tokens_per_block - 1) / a.tokens_per_block, (n_heads + hpb - 1) / hpb, splits);
   if (grid.y > 65535) return LLMI_ERR_BAD_SIZE;
   const int ldk = C + R + LM_PAD;
-  const size_t smem = (size_t)(row_groups * LM_ROWS + 2 * LM_KEYS) * ldk * 2 +
+  const size_t smem = (size_t)(row_groups * LM_ROWS + a.page_buffers * LM_KEYS) * ldk * 2 +
                       (size_t)row_groups * (LM_ROWS * (LM_KEYS + LM_PAD) * 2 + 2 * LM_WARPS * LM_ROWS * 4);
   int rc;
   switch (C / 32) {

@@ -7,7 +7,7 @@
 //   llmi_moe_up_grouped  tile x 64 columns: a = act(h Wgᵀ) * (h Wuᵀ) for the tile's gathered token rows   -> bf16 [items, F]
 //   llmi_moe_down_grouped tile x 64 columns: y = a Wdᵀ                                                     -> fp32 [items, W]
 //   llmi_moe_combine     per token: sum over its choices, in the order of the choice, of weight * y[item]   -> fp32 [T, W]
-// mma.sync m16n8k16 (bf16 in, fp32 accumulate), operands by cp.async through three stages.  A row's result does not
+// mma.sync m16n8k16 (bf16 in, fp32 accumulate), operands by cp.async through three stages of 64 k.  A row's result does not
 // depend on which tile or where in a tile it lies, and the combine adds in the order of the choice: a token's output
 // does not depend on its batch.  Needs W % 8 == 0 and F % 8 == 0 (16-byte rows); bf16 only.
 #include <math.h>
@@ -17,7 +17,9 @@
 
 namespace llmi {
 
-constexpr int GB_M = 64, GB_N = 64, GB_K = 32, GB_LD = GB_K + 8, GB_STAGES = 3;
+constexpr int GB_M = 64, GB_N = 64, GB_K = 64, GB_LD = GB_K + 8, GB_STAGES = 3;
+constexpr int GB_CH = GB_K / 8;            // 16-byte pieces of a tile row
+constexpr int GB_SLOTS = GB_M * GB_CH / 128;   // pieces a thread copies per operand and stage
 
 // meta: [0] number of tiles; offsets [E + 1]; tile_expert, tile_row0 [max_tiles]
 __global__ void __launch_bounds__(1024)
@@ -87,15 +89,15 @@ moe_grouped_kernel(const __nv_bfloat16* __restrict__ A, long lda, const int32_t*
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
   const int wm = warp >> 1, wn = warp & 1;
 
-  // the two (row, 8-element chunk) slots of a 64 x 32 tile that this thread copies
-  const __nv_bfloat16* a_src[2];
-  const __nv_bfloat16* b_src[NB][2];
-  int slot_r[2], slot_c[2];
+  // the (row, 8-element piece) slots of a 64 x GB_K tile that this thread copies
+  const __nv_bfloat16* a_src[GB_SLOTS];
+  const __nv_bfloat16* b_src[NB][GB_SLOTS];
+  int slot_r[GB_SLOTS], slot_c[GB_SLOTS];
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
+  for (int i = 0; i < GB_SLOTS; ++i) {
     const int s = tid + 128 * i;
-    slot_r[i] = s >> 2;
-    slot_c[i] = (s & 3) * 8;
+    slot_r[i] = s / GB_CH;
+    slot_c[i] = (s % GB_CH) * 8;
     const int r = slot_r[i];
     if (r < rows_here) {
       const long src_row = MODE == 0 ? (long)(sorted_items[row0 + r] / top) : (long)(row0 + r);
@@ -110,7 +112,7 @@ moe_grouped_kernel(const __nv_bfloat16* __restrict__ A, long lda, const int32_t*
   auto load = [&](int stage, int k0) {
     __nv_bfloat16* base = sm + (size_t)stage * STAGE;
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < GB_SLOTS; ++i) {
       const int k = k0 + slot_c[i];
       const bool k_ok = k < K;
       __nv_bfloat16* dst = base + slot_r[i] * GB_LD + slot_c[i];
@@ -257,6 +259,7 @@ LLMI_EXPORT int llmi_moe_grouped(const void* h, long ldh, const void* wg, const 
   if (!configured.here()) {
     cudaFuncSetAttribute(moe_grouped_kernel<0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_up);
     cudaFuncSetAttribute(moe_grouped_kernel<0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_up);
+    cudaFuncSetAttribute(moe_grouped_kernel<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);
     configured.here() = true;
   }
   if (act == 0)
@@ -286,6 +289,11 @@ LLMI_EXPORT int llmi_linear_heads_mma(const void* x, long ldx, long bx, const vo
   dim3 grid((M + GB_M - 1) / GB_M, (N + GB_N - 1) / GB_N, batch);
   if (grid.y > 65535) return LLMI_ERR_BAD_SIZE;
   const size_t smem = (size_t)GB_STAGES * 2 * GB_M * GB_LD * 2;
+  static PerDevice<bool> configured;
+  if (!configured.here()) {
+    cudaFuncSetAttribute(moe_grouped_kernel<2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    configured.here() = true;
+  }
   const __nv_bfloat16* wb = (const __nv_bfloat16*)w;
   return launch_pdl(PDL_GEMM, moe_grouped_kernel<2, 0>, grid, dim3(128), smem, stream, (const __nv_bfloat16*)x, ldx,
                     (const int32_t*)nullptr, 1, wb, wb, N, K, (const int32_t*)nullptr, (const int32_t*)nullptr, (const int32_t*)nullptr,

@@ -9,7 +9,7 @@ kv_heads).  Per head, in this order:
     S <- g S;   u = beta (v - Sᵀ k);   S <- S + k uᵀ;   o = Sᵀ q
 
 then o / rms(o) (over vdim) * weight * silu(W_g h), and W_o.  The state of a sequence — S [heads, dim, vdim] and the
-last conv-1 inputs of the convolution, all fp32 — lives in the cache's state slab, zero at the start; everything
+last conv-1 inputs of the convolution, all fp32 — lives in the cache's state slab (S column by column), zero at the start; everything
 behind the projections is fp32 (csrc/delta_rule.cu).
 """
 from __future__ import annotations
