@@ -55,7 +55,11 @@ WIDE = config(128, 300, [("latent_attention", att(4, 64, 32, 64, 128, 64), dense
                          ("delta", delta(4, 2, 128, 64, 4), moe(128, 8, 3)),
                          ("latent_attention", att(8, 32, 32, 32, 64, 64), moe(64, 4, 2)),
                          ("delta", delta(2, 1, 64, 128, 3), dense(192))], loop=(0, 2, 2), scale=1.0)
-CONFIGS = {"att": ATT_ONLY, "delta": DELTA_ONLY, "delta_reg": DELTA_REG, "dense": DENSE_ONLY, "moe": MOE_ONLY,
+# sizes that fit no fast kernel: rows of odd byte counts, head counts that divide nothing, a rotation of two entries
+ODD = config(36, 77, [("delta", delta(3, 3, 12, 10, 2), moe(10, 3, 2)),
+                      ("latent_attention", att(5, 6, 4, 7, 10, 9, rot_dims=2, base=77.0), dense(22)),
+                      ("latent_attention", att(1, 10, 2, 3, 6, 5), None)], loop=(0, 2, 2), scale=0.7, eps=1e-4)
+CONFIGS = {"odd": ODD, "att": ATT_ONLY, "delta": DELTA_ONLY, "delta_reg": DELTA_REG, "dense": DENSE_ONLY, "moe": MOE_ONLY,
            "moe_all": MOE_ALL, "looped": LOOPED, "loop_one": LOOP_ONE, "loop_once": LOOP_ONCE, "wide": WIDE}
 
 
