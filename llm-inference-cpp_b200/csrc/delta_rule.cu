@@ -7,9 +7,9 @@
 // ([head][column j][entry d]): the threads that share a column read and write neighbouring words.
 //
 // Everything here is fp32 arithmetic.  Kernels, in the order of a step:
-//   llmi_delta_prepare      per token: convolution + silu, unit norms, beta, decay          (parallel over tokens)
+//   llmi_delta_prepare      per (token, piece): convolution + silu, unit norms, beta, decay (parallel over tokens)
 //   llmi_delta_conv_carry   per sequence: the convolution's inputs that the next step needs (after prepare)
-//   llmi_delta_recurrence   per (sequence, head): the recurrence over the step's tokens, one thread per column of S
+//   llmi_delta_recurrence   per (sequence, head, slice of columns): the recurrence over the step's tokens
 //   llmi_delta_finish       per (token, head): o / rms(o) * w * silu(gate) in the compute type (parallel over tokens)
 // The input `proj` is one fp32 row per token: [ q (Hk*D) | k (Hk*D) | v (H*Dv) | b (H) | a (H) | gate (H*Dv) ].
 // The recurrence treats a column of S alone, and a step only continues what the slab holds: the result does not

@@ -58,7 +58,7 @@ WIDE = config(128, 300, [("latent_attention", att(4, 64, 32, 64, 128, 64), dense
 # sizes that fit no fast kernel: rows of odd byte counts, head counts that divide nothing, a rotation of two entries
 ODD = config(36, 77, [("delta", delta(3, 3, 12, 10, 2), moe(10, 3, 2)),
                       ("latent_attention", att(5, 6, 4, 7, 10, 9, rot_dims=2, base=77.0), dense(22)),
-                      ("latent_attention", att(1, 10, 2, 3, 6, 5), None)], loop=(0, 2, 2), scale=0.7, eps=1e-4)
+                      ("latent_attention", att(1, 10, 0, 3, 6, 5), None)], loop=(0, 2, 2), scale=0.7, eps=1e-4)      # the last: no rotated part at all
 CONFIGS = {"odd": ODD, "att": ATT_ONLY, "delta": DELTA_ONLY, "delta_reg": DELTA_REG, "dense": DENSE_ONLY, "moe": MOE_ONLY,
            "moe_all": MOE_ALL, "looped": LOOPED, "loop_one": LOOP_ONE, "loop_once": LOOP_ONCE, "wide": WIDE}
 
