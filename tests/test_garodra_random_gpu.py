@@ -1,0 +1,73 @@
+"""Random Garodra configurations — layer order, sizes, loop, constants and weights drawn per seed — with randomly cut
+traces, in 32 bits against the plain implementation (GPU).  What the fixed configurations of test_garodra_gpu.py happen
+not to combine shows up here."""
+import numpy as np
+import pytest
+
+import garodra_models as M
+import helpers as H
+import plain_garodra as G
+
+pytestmark = pytest.mark.gpu
+
+
+def random_config(rng):
+    width = int(rng.choice([24, 32, 40, 64, 96]))
+    layers = []
+    for _ in range(int(rng.integers(2, 6))):
+        if rng.random() < 0.5:
+            rot_dim = int(rng.choice([0, 2, 4, 8, 16]))
+            rot_dims = int(rng.choice([d for d in (0, 2, 4, 8, 16) if d <= rot_dim]))
+            mixer = ("latent_attention", M.att(int(rng.integers(1, 7)), int(rng.choice([4, 8, 12, 16, 32])), rot_dim,
+                                               int(rng.choice([4, 8, 10, 16])), int(rng.choice([8, 12, 16, 32, 64])),
+                                               int(rng.choice([6, 8, 16, 24])), rot_dims=rot_dims,
+                                               base=float(rng.choice([100.0, 10000.0, 500000.0])),
+                                               scale=float(rng.uniform(0.1, 0.5))))
+        else:
+            kv = int(rng.integers(1, 4))
+            mixer = ("delta", M.delta(kv * int(rng.integers(1, 3)), kv, int(rng.choice([8, 12, 16, 32, 64])),
+                                      int(rng.choice([6, 8, 16, 32, 48])), int(rng.integers(1, 6))))
+        r = rng.random()
+        if r < 0.4:
+            mlp = M.dense(int(rng.choice([16, 24, 40, 64])))
+        elif r < 0.8:
+            e = int(rng.integers(2, 9))
+            mlp = M.moe(int(rng.choice([8, 16, 24])), e, int(rng.integers(1, e + 1)))
+        else:
+            mlp = None
+        layers.append((*mixer, mlp))
+    loop = None
+    if rng.random() < 0.7:
+        a = int(rng.integers(0, len(layers)))
+        b = int(rng.integers(a + 1, len(layers) + 1))
+        loop = (a, b, int(rng.integers(1, 4)))
+    return M.config(width, int(rng.integers(30, 200)), layers, loop=loop, scale=float(rng.uniform(0.5, 3.0)),
+                    eps=float(rng.choice([1e-6, 1e-5, 1e-3])))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", range(10))
+def test_random_configuration_and_trace(seed, dtype, tmp_path):
+    import llmi_b200 as L
+    rng = np.random.default_rng(1000 + seed)
+    cfg = random_config(rng)
+    d = str(tmp_path / "m")
+    w = M.write_model(d, cfg, M.make_weights(cfg, seed, keep_state=bool(seed % 2)), {"float32": "F32", "bfloat16": "BF16"}[dtype])
+    model = L.load(d, dtype)
+    lengths = [int(n) for n in rng.integers(1, 150, 4)] + [int(rng.choice([63, 64, 65, 128, 129]))]
+    reqs = {f"r{i}": rng.integers(0, cfg["vocab"], n).tolist() for i, n in enumerate(lengths)}
+    refs = {r: G.forward(cfg, w, t) for r, t in reqs.items()}
+    cuts = [H.trace_whole(reqs), H.trace_portions(reqs, int(rng.integers(2, 40)), n_last=int(rng.integers(1, 20))),
+            H.trace_batches(reqs, int(rng.integers(2, 5)), {r: int(rng.integers(1, len(t) + 1)) for r, t in reqs.items()}),
+            H.trace_mixed(reqs, {r: int(rng.integers(1, len(t) + 1)) for r, t in reqs.items()},
+                          {r: int(rng.choice([1, 1, 2, 9])) for r in reqs})]
+    for steps, most in cuts:
+        got = H.collect(steps, H.replay(model, steps, most), cfg["vocab"])
+        errs = []
+        for r in refs:
+            assert np.isfinite(got[r]).all(), (cfg, r)
+            errs.extend((np.abs(got[r] - refs[r]).max(axis=1) / np.abs(refs[r]).max()).tolist())
+        if dtype == "float32":
+            assert max(errs) < 5e-5, (cfg, max(errs))
+        else:       # bf16: a router's close call may go the other way for some rows; the typical row is close
+            assert float(np.median(errs)) < 2e-2, (cfg, float(np.median(errs)))
