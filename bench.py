@@ -2,6 +2,8 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --workload smollm2-360m|smollm2-135m [--workload-dtypes bfloat16,float32]
+    python bench.py --design garodra [--design-sizes 2048,1024,2048-looped]      (its own JSON line: that design's prefill and
+                                                                                  decode beside the Llama decoder at equal size)
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 and context 4096 (a
 "step" is one decode step of the whole batch), timed on the device with CUDA events around

@@ -21,7 +21,7 @@ def random_config(rng):
             mixer = ("latent_attention", M.att(int(rng.integers(1, 7)), int(rng.choice([4, 8, 12, 16, 32])), rot_dim,
                                                int(rng.choice([4, 8, 10, 16])), int(rng.choice([8, 12, 16, 32, 64])),
                                                int(rng.choice([6, 8, 16, 24])), rot_dims=rot_dims,
-                                               base=float(rng.choice([100.0, 10000.0, 500000.0])),
+                                               base=float(rng.choice([100.0, 10000.0, 1000000.0])),
                                                scale=float(rng.uniform(0.1, 0.5))))
         else:
             kv = int(rng.integers(1, 4))
