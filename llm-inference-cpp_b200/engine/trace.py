@@ -19,10 +19,16 @@ from .batch import SequenceStep
 from .loader import load_model
 
 
+SPARE_PAGES = 64     # every live request may leave most of its last page unused: room for that many requests beyond max_tokens
+
+
 class TraceReplayer:
-    def __init__(self, model, max_tokens: int):
+    def __init__(self, model, max_tokens: int, spare_pages: int = SPARE_PAGES):
+        """``max_tokens``: the most tokens live requests hold at once, padding not counted; the cache is sized for them
+        in whole pages plus ``spare_pages`` pages for the requests' partly filled last pages."""
         self.model = model
-        self.cache = model.new_cache(max(max_tokens, PAGE_SIZE))
+        pages = (max(max_tokens, 1) + PAGE_SIZE - 1) // PAGE_SIZE + max(spare_pages, 0)
+        self.cache = model.new_cache(pages * PAGE_SIZE)
         self.slots: dict[str, int] = {}
 
     def run_step(self, step: dict):
@@ -53,7 +59,8 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help=f"most tokens live requests hold at once (each rounded up to {PAGE_SIZE})")
+                    help=f"most tokens live requests hold at once, padding not counted (the cache keeps {SPARE_PAGES} pages "
+                         f"of {PAGE_SIZE} beyond that for partly filled last pages)")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
     os.makedirs(args.out, exist_ok=True)

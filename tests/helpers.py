@@ -117,7 +117,7 @@ def replay(model, steps, max_tokens, poison=True):
     """Run a trace in-process through the library's TraceReplayer; returns the per-step logits."""
     import torch
     from llmi_b200.engine.trace import TraceReplayer
-    rp = TraceReplayer(model, max_tokens)
+    rp = TraceReplayer(model, max_tokens, spare_pages=0)     # exactly what the trace needs: freed pages and slots must be used again
     if poison:      # whatever is read outside a sequence's own positions turns the logits to NaN
         for g in rp.cache.kv_groups:
             g.k.fill_(float("nan"))

@@ -166,6 +166,7 @@ def test_programs_as_a_user_calls_them(loaded, tmp_path):
     reqs = requests_for(cfg, [5, 70, 33])
     steps, most = H.trace_batches(reqs, 3, {"r0": 2, "r1": 40, "r2": 33})
     out = tmp_path / "out"
+    most = sum(len(t) for t in reqs.values())           # the raw count, padding not counted: their last pages are partly filled
     p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype", "float32",
                         "--out", str(out), "--max-tokens", str(most)],
                        input="".join(json.dumps(s_) + "\n" for s_ in steps), capture_output=True, text=True, timeout=600)

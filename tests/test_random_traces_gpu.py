@@ -67,7 +67,7 @@ def test_random_configuration_and_trace(tmp_path, seed, dtype):
     reqs = {f"r{i}": rng.integers(0, V, n).tolist() for i, n in enumerate(lengths)}
     refs = {r: P.forward(c, w, t) for r, t in reqs.items()}
     steps = random_trace(rng, reqs)
-    rp = TraceReplayer(model, 3 * 576)
+    rp = TraceReplayer(model, 3 * 576, spare_pages=0)
     for g in rp.cache.kv_groups:
         g.k.fill_(float("nan"))
         g.v.fill_(float("nan"))
