@@ -6,7 +6,9 @@ A mixer says what it needs per sequence with a *request*:
   ``n_kv_heads × head_dim`` each.  Calls with equal requests share a *group*: one
   page pool and one pair of tensors ``[calls, pages, kv_heads, page_size, head_dim]``
   (one (page, kv head) tile is contiguous — head-major within the page, after the
-  reference's layout, include/llmi/model/transformer.hpp:39-44).
+  reference's layout, include/llmi/model/transformer.hpp:39-44).  Values may have a
+  head count and a head size of their own (``v_heads``, ``v_dim``): the V tensor is then
+  ``[calls, pages, v_heads, page_size, v_dim]`` over the same pages.
 * :class:`StateRequest` — a fixed-size state per sequence, ``[calls, slots, *shape]``,
   zeroed when a slot is handed out.  The Llama architecture asks for none; the slab is
   here so that a mixer with a recurrent state needs no change of the cache.
@@ -16,7 +18,7 @@ Groups with different requests have storage and page pools of their own.
 from __future__ import annotations
 
 import itertools
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 
 import numpy as np
 import torch
@@ -30,6 +32,8 @@ class KVRequest:
     head_dim: int
     window: int = 0          # 0: all positions
     values: bool = True      # False: keys only (a mixer whose values are part of its key rows)
+    v_heads: int = 0         # value heads and their size, where they differ from the keys' (0: as the keys)
+    v_dim: int = 0
 
 
 @dataclass(frozen=True)
@@ -40,10 +44,14 @@ class StateRequest:
 
 @dataclass
 class CacheBinding:
-    """What one scheduled call holds of the cache: its group and its index inside the group."""
+    """What one scheduled call holds of the cache: its group and its index inside the group.  ``more`` holds the
+    bindings of the layer's further parts that keep something per sequence (slot name -> CacheBinding): a short
+    convolution ahead of the mixer, say.  Those are always the call's own, also where the mixer reads another call's
+    cache."""
     group: object
     index: int
     writes: bool = True      # False: the call reads another call's entries
+    more: dict = field(default_factory=dict)
 
 
 class KVGroup:
@@ -55,11 +63,14 @@ class KVGroup:
         self.pool = PagePool(n_pages, page_size, request.window, n_slots, max_pages_per_slot)
         shape = (n_calls, n_pages, request.n_kv_heads, page_size, request.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device) if request.values else None
+        self.v_heads, self.v_dim = request.v_heads or request.n_kv_heads, request.v_dim or request.head_dim
+        v_shape = (n_calls, n_pages, self.v_heads, page_size, self.v_dim)
+        self.v = torch.zeros(v_shape, dtype=dtype, device=device) if request.values else None
 
     def bytes_per_token(self) -> int:
         r = self.request
-        return (2 if r.values else 1) * self.n_calls * r.n_kv_heads * r.head_dim * self.k.element_size()
+        per = r.n_kv_heads * r.head_dim + (self.v_heads * self.v_dim if r.values else 0)
+        return self.n_calls * per * self.k.element_size()
 
 
 class StateGroup:

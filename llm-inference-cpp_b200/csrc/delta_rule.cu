@@ -10,7 +10,7 @@
 //   llmi_delta_prepare      per (token, piece): convolution + silu, unit norms, beta, decay (parallel over tokens)
 //   llmi_delta_conv_carry   per sequence: the convolution's inputs that the next step needs (after prepare)
 //   llmi_delta_recurrence   per (sequence, head, slice of columns): the recurrence over the step's tokens
-//   llmi_delta_finish       per (token, head): o / rms(o) * w * silu(gate) in the compute type (parallel over tokens)
+//   llmi_delta_finish       per (token, head): o / rms(o) * w * act(gate) in the compute type (parallel over tokens)
 // The input `proj` is one fp32 row per token: [ q (Hk*D) | k (Hk*D) | v (H*Dv) | b (H) | a (H) | gate (H*Dv) ].
 // The recurrence treats a column of S alone, and a step only continues what the slab holds: the result does not
 // depend on how a prompt was cut or on what else is in the batch.
@@ -363,12 +363,13 @@ int launch_delta_recurrence_quad(const float* prep, long ldp, DeltaDims m, float
                     ldp, m, state, seq_q_start, seq_slot, o_raw, ldo, write_state);
 }
 
-// One warp per (token, head): out = o / sqrt(mean(o^2) + eps) * w * silu(gate).
+// One warp per (token, head): out = o / sqrt(mean(o^2) + eps) * w * act(gate); w is one vector for all heads
+// (w_head_stride 0) or a vector per head (w_head_stride Dv); act: silu (0) or the logistic function (1).
 template <typename T>
 __global__ void __launch_bounds__(128)
 delta_finish_kernel(const float* __restrict__ o_raw, long ldo, const float* __restrict__ gate, long ldg,
-                    const float* __restrict__ w, float eps, int H, int Dv, const int32_t* __restrict__ tok_seq,
-                    T* __restrict__ out, long ld_out, long n_items) {
+                    const float* __restrict__ w_all, int w_head_stride, int gate_act, float eps, int H, int Dv,
+                    const int32_t* __restrict__ tok_seq, T* __restrict__ out, long ld_out, long n_items) {
   pdl_launch_dependents();
   pdl_wait();
   const long item = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -382,11 +383,13 @@ delta_finish_kernel(const float* __restrict__ o_raw, long ldo, const float* __re
   }
   const float* o = o_raw + (size_t)t * ldo + (size_t)h * Dv;
   const float* g = gate + (size_t)t * ldg + (size_t)h * Dv;
+  const float* w = w_all + (size_t)h * w_head_stride;
   float ss = 0.f;
   for (int d = lane; d < Dv; d += 32) ss = fmaf(o[d], o[d], ss);
   ss = warp_sum(ss);
   const float sc = 1.0f / sqrtf(ss / (float)Dv + eps);
-  for (int d = lane; d < Dv; d += 32) dst[d] = from_f32<T>(w[d] * (o[d] * sc) * silu_f(g[d]));
+  for (int d = lane; d < Dv; d += 32)
+    dst[d] = from_f32<T>(w[d] * (o[d] * sc) * (gate_act == 0 ? silu_f(g[d]) : 1.0f / (1.0f + expf(-g[d]))));
 }
 
 template <int DREG>
@@ -457,16 +460,17 @@ LLMI_EXPORT int llmi_delta_recurrence(const float* prep, long ldp, int H, int Hk
 }
 
 LLMI_EXPORT int llmi_delta_finish(int dtype, const float* o_raw, long ldo, const float* gate, long ldg, const float* w,
-                                  float eps, int H, int Dv, const int32_t* tok_seq, void* out, long ld_out, int n_tokens,
-                                  cudaStream_t stream) {
-  if (n_tokens <= 0 || H <= 0 || Dv <= 0) return LLMI_ERR_BAD_SIZE;
+                                  int w_head_stride, int gate_act, float eps, int H, int Dv, const int32_t* tok_seq, void* out,
+                                  long ld_out, int n_tokens, cudaStream_t stream) {
+  if (n_tokens <= 0 || H <= 0 || Dv <= 0 || (w_head_stride != 0 && w_head_stride != Dv)) return LLMI_ERR_BAD_SIZE;
+  if (gate_act != 0 && gate_act != 1) return LLMI_ERR_UNSUPPORTED;
   const long items = (long)n_tokens * H;
   const unsigned blocks = (unsigned)((items + 3) / 4);
   if (dtype == LLMI_DTYPE_F32)
-    return launch_pdl(PDL_SMALL, delta_finish_kernel<float>, blocks, 128, 0, stream, o_raw, ldo, gate, ldg, w, eps, H, Dv, tok_seq,
-                      (float*)out, ld_out, items);
+    return launch_pdl(PDL_SMALL, delta_finish_kernel<float>, blocks, 128, 0, stream, o_raw, ldo, gate, ldg, w, w_head_stride,
+                      gate_act, eps, H, Dv, tok_seq, (float*)out, ld_out, items);
   if (dtype == LLMI_DTYPE_BF16)
-    return launch_pdl(PDL_SMALL, delta_finish_kernel<__nv_bfloat16>, blocks, 128, 0, stream, o_raw, ldo, gate, ldg, w, eps, H, Dv,
-                      tok_seq, (__nv_bfloat16*)out, ld_out, items);
+    return launch_pdl(PDL_SMALL, delta_finish_kernel<__nv_bfloat16>, blocks, 128, 0, stream, o_raw, ldo, gate, ldg, w,
+                      w_head_stride, gate_act, eps, H, Dv, tok_seq, (__nv_bfloat16*)out, ld_out, items);
   return LLMI_ERR_BAD_DTYPE;
 }

@@ -1,4 +1,4 @@
-// Row-wise kernels: embedding gather, RMSNorm, SwiGLU gating.
+// Row-wise kernels: embedding gather, RMSNorm, SwiGLU gating, plain activations.
 //
 // Formulas (reference, CPU): embedding row copy src/model/weight.cpp:39-45 and
 // src/model/transformer.cpp:214-217; RMSNorm src/model/kernels.cpp:115-120
@@ -166,6 +166,17 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
   }
 }
 
+// out = act(x), elementwise; act 0: relu(x)^2.
+template <typename T>
+__global__ void activate_kernel(const T* __restrict__ x, T* __restrict__ out, int act, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const float v = fmaxf(to_f32(x[i]), 0.f);
+    out[i] = from_f32<T>(v * v);
+  }
+}
+
 }  // namespace llmi
 
 using namespace llmi;
@@ -260,4 +271,19 @@ LLMI_EXPORT int llmi_swiglu(int dtype, const void* gate_up, void* out, int n_row
   else
     return LLMI_ERR_BAD_DTYPE;
   return launch_status();
+}
+
+LLMI_EXPORT int llmi_activate(int dtype, const void* x, void* out, long total, int act, cudaStream_t stream) {
+  if (total <= 0) return LLMI_ERR_BAD_SIZE;
+  if (act != 0) return LLMI_ERR_UNSUPPORTED;
+  const int threads = 256;
+  const size_t most = (size_t)sm_count() * 16;       // a grid-stride loop takes the rest
+  const size_t want = ((size_t)total + threads - 1) / threads;
+  const int blocks = (int)(want < most ? want : most);
+  if (dtype == LLMI_DTYPE_F32)
+    return launch_pdl(PDL_SMALL, activate_kernel<float>, blocks, threads, 0, stream, (const float*)x, (float*)out, act, (size_t)total);
+  if (dtype == LLMI_DTYPE_BF16)
+    return launch_pdl(PDL_SMALL, activate_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16*)x,
+                      (__nv_bfloat16*)out, act, (size_t)total);
+  return LLMI_ERR_BAD_DTYPE;
 }

@@ -1,0 +1,104 @@
+// A short causal convolution over time on every channel of a step's rows, added to its own input:
+//     y[t, c] = h[t, c] + sum_{j < K} w[c, j] * h[t - (K-1) + j, c]          (zeros before a sequence's start)
+// The K-1 rows ahead of a step's first token come from the sequence's state (`carry`, fp32, [K-1][C] per slot:
+// the inputs at positions p0-(K-1) .. p0-1), which a second kernel brings up to date after the step.  The sum is
+// fp32, taps in the order oldest first, so a position's result does not depend on how its sequence was cut.
+//
+//   llmi_conv_add     one thread per (token, channel)
+//   llmi_conv_carry   one thread per (sequence, channel): the inputs of the last K-1 positions after this step,
+//                     from the step's own rows or, where the step brought fewer, from what the state held
+#include "common.cuh"
+
+namespace llmi {
+
+constexpr int CONV_MAX_TAPS = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+conv_add_kernel(const T* __restrict__ h, long ldh, const float* __restrict__ w, const float* __restrict__ carry_all,
+                long carry_stride, const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ tok_pos,
+                const int32_t* __restrict__ seq_q_start, const int32_t* __restrict__ seq_slot, T* __restrict__ y, long ldy,
+                int C, int K) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int seq = tok_seq[t];
+  if (seq < 0) {
+    y[(size_t)t * ldy + c] = from_f32<T>(0.f);
+    return;
+  }
+  const int slot = seq_slot[seq];
+  const int pos = tok_pos[t], r0 = seq_q_start[seq];
+  const int p0 = pos - (t - r0);                              // position of this sequence's first row of the step
+  const float* carry = carry_all + (size_t)(slot < 0 ? 0 : slot) * carry_stride;
+  const float own = to_f32(h[(size_t)t * ldh + c]);
+  float acc = 0.f;
+  for (int j = 0; j < K; ++j) {                               // oldest tap first
+    const int p = pos - (K - 1) + j;
+    if (p < 0) continue;
+    const float x = p >= p0 ? to_f32(h[(size_t)(r0 + (p - p0)) * ldh + c]) : carry[(size_t)(p - (p0 - (K - 1))) * C + c];
+    acc = fmaf(x, w[(size_t)c * K + j], acc);
+  }
+  y[(size_t)t * ldy + c] = from_f32<T>(own + acc);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+conv_carry_kernel(const T* __restrict__ h, long ldh, float* __restrict__ carry_all, long carry_stride,
+                  const int32_t* __restrict__ seq_q_start, const int32_t* __restrict__ seq_kv_len,
+                  const int32_t* __restrict__ seq_slot, int C, int K) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int seq = blockIdx.y;
+  const int slot = seq_slot[seq];
+  if (slot < 0) return;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int r0 = seq_q_start[seq], n = seq_q_start[seq + 1] - r0, L = seq_kv_len[seq];
+  if (n <= 0) return;
+  const int p0 = L - n;
+  float* carry = carry_all + (size_t)slot * carry_stride;
+  float keep[CONV_MAX_TAPS];
+  for (int j = 0; j < K - 1; ++j) {
+    const int p = L - (K - 1) + j;
+    keep[j] = p < 0 ? 0.f
+                    : (p >= p0 ? to_f32(h[(size_t)(r0 + (p - p0)) * ldh + c]) : carry[(size_t)(p - (p0 - (K - 1))) * C + c]);
+  }
+  for (int j = 0; j < K - 1; ++j) carry[(size_t)j * C + c] = keep[j];
+}
+
+}  // namespace llmi
+
+using namespace llmi;
+
+// y = h + conv(h); h, y [T, C] in the type `dtype`; w fp32 [C, K]; carry fp32 [slots, carry_stride >= (K-1)*C].
+LLMI_EXPORT int llmi_conv_add(int dtype, const void* h, long ldh, const float* w, const float* carry, long carry_stride,
+                              const int32_t* tok_seq, const int32_t* tok_pos, const int32_t* seq_q_start,
+                              const int32_t* seq_slot, void* y, long ldy, int n_tokens, int C, int K, cudaStream_t stream) {
+  if (n_tokens <= 0 || C <= 0 || (C + 127) / 128 > 65535 || K < 1 || K > CONV_MAX_TAPS) return LLMI_ERR_BAD_SIZE;
+  const dim3 grid(n_tokens, (C + 127) / 128);
+  if (dtype == LLMI_DTYPE_F32)
+    return launch_pdl(PDL_SMALL, conv_add_kernel<float>, grid, dim3(128), 0, stream, (const float*)h, ldh, w, carry, carry_stride,
+                      tok_seq, tok_pos, seq_q_start, seq_slot, (float*)y, ldy, C, K);
+  if (dtype == LLMI_DTYPE_BF16)
+    return launch_pdl(PDL_SMALL, conv_add_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)h, ldh, w, carry,
+                      carry_stride, tok_seq, tok_pos, seq_q_start, seq_slot, (__nv_bfloat16*)y, ldy, C, K);
+  return LLMI_ERR_BAD_DTYPE;
+}
+
+LLMI_EXPORT int llmi_conv_carry(int dtype, const void* h, long ldh, float* carry, long carry_stride, const int32_t* seq_q_start,
+                                const int32_t* seq_kv_len, const int32_t* seq_slot, int n_seqs, int C, int K,
+                                cudaStream_t stream) {
+  if (n_seqs <= 0 || n_seqs > 65535 || C <= 0 || K < 1 || K > CONV_MAX_TAPS) return LLMI_ERR_BAD_SIZE;
+  if (K == 1) return LLMI_OK;
+  const dim3 grid((C + 127) / 128, n_seqs);
+  if (dtype == LLMI_DTYPE_F32)
+    return launch_pdl(PDL_SMALL, conv_carry_kernel<float>, grid, dim3(128), 0, stream, (const float*)h, ldh, carry, carry_stride,
+                      seq_q_start, seq_kv_len, seq_slot, C, K);
+  if (dtype == LLMI_DTYPE_BF16)
+    return launch_pdl(PDL_SMALL, conv_carry_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)h, ldh, carry,
+                      carry_stride, seq_q_start, seq_kv_len, seq_slot, C, K);
+  return LLMI_ERR_BAD_DTYPE;
+}

@@ -45,7 +45,7 @@ class Model:
         parts += [e for e in self.entries if e is not None]
         self.pads_prompts = dtype == torch.bfloat16 and all(getattr(p, "takes_padding_rows", False) for p in parts)
         self.last_logits = None      # fp32 [rows, vocab] of the latest step_and_choose (scratch: valid until the next step)
-        self.parameter_count = sum(int(torch.tensor(d.shape).prod()) for d in expected_tensors(spec).values())
+        self.parameter_count = sum(int(tensors[n].numel()) if n in tensors else 0 for n in expected_tensors(spec))
 
     # -- sizes -----------------------------------------------------------------------------
     @property
@@ -79,18 +79,25 @@ class Model:
         requests = [self.layers[c.layer].mixer.cache_request() for c in self.spec.schedule]
         kv_groups: dict = {}
         state_groups: dict = {}
-        place = []
-        for i, (call, req) in enumerate(zip(self.spec.schedule, requests)):
-            if call.cache_of is not None:
-                place.append(None)
-                continue
+
+        def take(req, owner):
+            """A place for one request: (kind, request, index in its group)."""
             table = kv_groups if isinstance(req, KVRequest) else state_groups if isinstance(req, StateRequest) else None
             if table is None:
-                place.append(("none", None, 0))
-                continue
+                return ("none", None, 0)
             table.setdefault(req, [])
-            place.append(("kv" if table is kv_groups else "state", req, len(table[req])))
-            table[req].append(i)
+            table[req].append(owner)
+            return ("kv" if table is kv_groups else "state", req, len(table[req]) - 1)
+
+        place = []
+        for i, (call, req) in enumerate(zip(self.spec.schedule, requests)):
+            place.append(None if call.cache_of is not None else take(req, i))
+        # further parts of a layer that keep something per sequence (every call has its own)
+        more_places = []
+        for i, call in enumerate(self.spec.schedule):
+            layer = self.layers[call.layer]
+            more_places.append({slot: take(p.cache_request(), (i, slot)) for slot, p in layer.parts.items()
+                                if slot != "mixer" and hasattr(p, "cache_request")})
         cache = SequenceCache([(r, len(c)) for r, c in kv_groups.items()],
                               [(r, len(c)) for r, c in state_groups.items()],
                               max_tokens, self.spec.max_positions, self.rt.dtype, self.rt.device, n_slots=n_slots)
@@ -105,7 +112,9 @@ class Model:
             if call.cache_of is not None and requests[i] != req:
                 raise ValueError(f"schedule call {i} cannot read the cache of call {call.cache_of}: their needs differ")
             group = kv_index[req] if kind == "kv" else st_index[req] if kind == "state" else None
-            bindings.append(CacheBinding(group, idx, writes=call.cache_of is None))
+            more = {slot: CacheBinding(kv_index[r] if k == "kv" else st_index[r] if k == "state" else None, j)
+                    for slot, (k, r, j) in more_places[i].items()}
+            bindings.append(CacheBinding(group, idx, writes=call.cache_of is None, more=more))
         cache.bindings = bindings
         cache.owner = self
         # the (mixer, binding) pairs whose launches may depend on more than a step's padded shape, one of a kind

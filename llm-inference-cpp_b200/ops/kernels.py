@@ -155,7 +155,9 @@ def lib():
                      "llmi_sm_count", "llmi_dyt", "llmi_dyt_add", "llmi_stream_add", "llmi_linear_simt_batched",
                      "llmi_latent_prepare", "llmi_latent_q_rotate", "llmi_attention_latent", "llmi_delta_prepare",
                      "llmi_delta_conv_carry", "llmi_delta_recurrence", "llmi_delta_finish", "llmi_moe_route", "llmi_moe_up",
-                     "llmi_moe_down", "llmi_moe_grouped", "llmi_linear_heads_mma", "llmi_attention_latent_mma", "llmi_attention_latent_mma_supported"):
+                     "llmi_moe_down", "llmi_moe_grouped", "llmi_linear_heads_mma", "llmi_attention_latent_mma", "llmi_attention_latent_mma_supported",
+                     "llmi_conv_add", "llmi_conv_carry", "llmi_qkv_prepare", "llmi_attention_flex", "llmi_diff_combine",
+                     "llmi_gdelta_prepare", "llmi_dplr_recurrence", "llmi_activate"):
             getattr(l, name).restype = c_int
         l.llmi_gemm_tc_workspace.restype = c_long
         l.llmi_delta_state_floats.restype = c_long
@@ -826,6 +828,106 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, seq_p
 
 
 # ---------------------------------------------------------------------------------------------
+# Attention in its general form (csrc/qkv_prepare.cu, csrc/attention_flex.cu)
+
+def qkv_prepare(proj: torch.Tensor, n_q_heads: int, n_k_heads: int, dk: int, n_v_heads: int, dv: int, q_norm_w, k_norm_w,
+                eps: float, inv_freq, rot_dims: int, ctx, seq_pages, page_size: int, k_cache, v_cache, q_out: torch.Tensor,
+                has_kv: bool = True, write_kv: bool = True) -> None:
+    """From the fp32 rows [q | k | v] of a step (k, v absent without ``has_kv``): optional RMS norms over the whole q
+    part and the whole k part (weights ``q_norm_w``, ``k_norm_w``), rotation of the first ``rot_dims`` entries of every
+    q and k head, q into ``q_out`` (compute type), k and v into their cache pages."""
+    _need_cuda(proj, q_norm_w, k_norm_w, inv_freq, seq_pages, k_cache, v_cache, q_out)
+    T = proj.shape[0]
+    n_in = n_q_heads * dk + ((n_k_heads * dk + n_v_heads * dv) if has_kv else 0)
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] >= n_in
+    assert q_out.shape == (T, n_q_heads * dk) and q_out.stride(1) == 1 and seq_pages.dtype == torch.int32
+    for wt, n in ((q_norm_w, n_q_heads * dk), (k_norm_w, n_k_heads * dk)):
+        assert wt is None or (wt.dtype == torch.float32 and wt.numel() == n and wt.is_contiguous())
+    if has_kv:
+        assert k_cache.dtype == v_cache.dtype == q_out.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+        assert k_cache.shape[-3:] == (n_k_heads, page_size, dk) and v_cache.shape[-3:] == (n_v_heads, page_size, dv)
+    if rot_dims:
+        assert inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() >= rot_dims // 2
+    _check("qkv_prepare", lib().llmi_qkv_prepare(
+        c_int(_dtype_code(q_out)), _ptr(proj), c_long(proj.stride(0)), c_int(n_q_heads), c_int(n_k_heads), c_int(dk),
+        c_int(n_v_heads), c_int(dv), _ptr(q_norm_w), _ptr(k_norm_w), c_float(eps), _ptr(inv_freq), c_int(rot_dims),
+        _ptr(ctx.tok_seq), _ptr(ctx.tok_pos), _ptr(seq_pages), c_int(seq_pages.stride(0)), _ptr(seq_pages),
+        c_int(seq_pages.stride(0)), c_int(page_size), _ptr(k_cache if has_kv else None), _ptr(v_cache if has_kv else None),
+        _ptr(q_out), c_long(q_out.stride(0)), c_int(T), c_int(1 if has_kv else 0), c_int(1 if write_kv else 0), _stream()))
+
+
+def attention_flex(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, seq_pages, page_size: int, n_heads: int,
+                   n_kv_heads: int, maps: int, dk: int, dv: int, scale: float, head_scale=None, window: int = 0,
+                   chunk: int = 0) -> None:
+    """Causal attention of every token over its sequence's cache with ``maps`` score maps per head (query row
+    [head][map][dk], key heads [kv head][map], one set of values [kv head][dv]); out [T, heads*maps*dv] in q's type or
+    fp32.  ``head_scale`` fp32 [heads] multiplies the scores of a head; ``window`` and ``chunk`` limit the visible keys
+    (a query at p sees max(p - window + 1, p // chunk * chunk) .. p)."""
+    _need_cuda(q, out, k_cache, v_cache, seq_pages, head_scale)
+    T = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape == (T, n_heads * maps * dv) and q.shape[1] >= n_heads * maps * dk
+    assert q.dtype == k_cache.dtype == v_cache.dtype and out.dtype in (q.dtype, torch.float32)
+    assert k_cache.shape[-3:] == (n_kv_heads * maps, page_size, dk) and v_cache.shape[-3:] == (n_kv_heads, page_size, dv)
+    assert head_scale is None or (head_scale.dtype == torch.float32 and head_scale.numel() == n_heads)
+    _check("attention_flex", lib().llmi_attention_flex(
+        c_int(_dtype_code(q)), _ptr(q), c_long(q.stride(0)), _ptr(out), c_long(out.stride(0)),
+        c_int(1 if out.dtype == torch.float32 else 0), _ptr(k_cache), _ptr(v_cache), _ptr(ctx.tok_seq), _ptr(ctx.tok_pos),
+        _ptr(seq_pages), c_int(seq_pages.stride(0)), c_int(page_size), c_int(T), c_int(n_heads), c_int(n_kv_heads), c_int(maps),
+        c_int(dk), c_int(dv), c_float(scale), _ptr(head_scale), c_int(window), c_int(chunk), _stream()))
+
+
+def attention_maps(q, out, k_cache, v_cache, ctx, seq_pages, page_size: int, n_heads: int, n_kv_heads: int, maps: int,
+                   dk: int, dv: int, scale: float, head_scale=None, window: int = 0, chunk: int = 0, rt=None) -> None:
+    """The attention of a step in its general form (arguments as :func:`attention_flex`): the kernel that takes the
+    step's sizes and type."""
+    attention_flex(q, out, k_cache, v_cache, ctx, seq_pages, page_size, n_heads, n_kv_heads, maps, dk, dv, scale, head_scale,
+                   window, chunk)
+
+
+def diff_combine(a: torch.Tensor, lam: float, eps: float, post: float, H: int, dv: int, ctx, out: torch.Tensor) -> None:
+    """out = (a1 - lam * a2) / rms(a1 - lam * a2) * post per (token, head); a fp32 [T, H*2*dv] ([head][map][dv])."""
+    _need_cuda(a, out)
+    T = a.shape[0]
+    assert a.dtype == torch.float32 and a.stride(1) == 1 and a.shape[1] == 2 * H * dv and out.shape == (T, H * dv) and out.stride(1) == 1
+    _check("diff_combine", lib().llmi_diff_combine(c_int(_dtype_code(out)), _ptr(a), c_long(a.stride(0)), c_float(lam), c_float(eps),
+                                                   c_float(post), c_int(H), c_int(dv), _ptr(ctx.tok_seq), _ptr(out),
+                                                   c_long(out.stride(0)), c_int(T), _stream()))
+
+
+# ---------------------------------------------------------------------------------------------
+# A short convolution over time with a carried state (csrc/short_conv.cu); plain activations
+
+def conv_add(h: torch.Tensor, w: torch.Tensor, carry: torch.Tensor, ctx, out: torch.Tensor, write_state: bool = True) -> None:
+    """out = h + conv(h): per channel a causal convolution over time with ``w`` fp32 [C, K]; the K-1 inputs ahead of a
+    step's first row come from ``carry`` fp32 [slots, >= (K-1)*C], which is then brought up to date."""
+    _need_cuda(h, w, carry, out)
+    T, C = h.shape
+    K = w.shape[1]
+    assert h.stride(1) == 1 and out.stride(1) == 1 and out.shape == (T, C) and out.dtype == h.dtype
+    assert w.dtype == torch.float32 and w.shape == (C, K) and w.is_contiguous()
+    assert carry.dtype == torch.float32 and carry.dim() == 2 and carry.stride(1) == 1 and carry.shape[1] >= (K - 1) * C
+    assert out.data_ptr() != h.data_ptr()
+    _check("conv_add", lib().llmi_conv_add(c_int(_dtype_code(h)), _ptr(h), c_long(h.stride(0)), _ptr(w), _ptr(carry),
+                                           c_long(carry.stride(0)), _ptr(ctx.tok_seq), _ptr(ctx.tok_pos), _ptr(ctx.seq_q_start),
+                                           _ptr(ctx.seq_slot), _ptr(out), c_long(out.stride(0)), c_int(T), c_int(C), c_int(K), _stream()))
+    if write_state and K > 1:
+        _check("conv_carry", lib().llmi_conv_carry(c_int(_dtype_code(h)), _ptr(h), c_long(h.stride(0)), _ptr(carry),
+                                                   c_long(carry.stride(0)), _ptr(ctx.seq_q_start), _ptr(ctx.seq_kv_len),
+                                                   _ptr(ctx.seq_slot), c_int(ctx.n_seqs), c_int(C), c_int(K), _stream()))
+
+
+ACT_RELU2 = 0
+PLAIN_ACTIVATIONS = {"relu2": ACT_RELU2}
+
+
+def activate(x: torch.Tensor, out: torch.Tensor, act: int = ACT_RELU2) -> None:
+    """out = act(x), elementwise (in place if out is x); act: the square of relu."""
+    _need_cuda(x, out)
+    assert x.is_contiguous() and out.is_contiguous() and x.shape == out.shape and x.dtype == out.dtype
+    _check("activate", lib().llmi_activate(c_int(_dtype_code(x)), _ptr(x), _ptr(out), c_long(x.numel()), c_int(act), _stream()))
+
+
+# ---------------------------------------------------------------------------------------------
 # Dynamic Tanh, and what a looped span adds to the stream
 
 def dyt(x: torch.Tensor, weight, bias, alpha: float, out: torch.Tensor, rows: torch.Tensor | None = None) -> None:
@@ -1004,16 +1106,56 @@ def delta_step(proj: torch.Tensor, dims, conv_w, a_log, dt_bias, state: torch.Te
                                                        c_int(1 if write_state else 0), _stream()))
 
 
-def delta_finish(o_raw: torch.Tensor, gate: torch.Tensor, weight, eps: float, H: int, Dv: int, ctx, out: torch.Tensor) -> None:
-    """out = o / rms(o) * weight * silu(gate) per (token, head); o_raw fp32 [T, H*Dv], gate fp32 [T, H*Dv] (a strided
-    view), out in the compute type."""
+GATE_SILU, GATE_SIGMOID = 0, 1
+
+
+def delta_finish(o_raw: torch.Tensor, gate: torch.Tensor, weight, eps: float, H: int, Dv: int, ctx, out: torch.Tensor,
+                 gate_act: int = GATE_SILU) -> None:
+    """out = o / rms(o) * weight * act(gate) per (token, head); o_raw fp32 [T, H*Dv], gate fp32 [T, H*Dv] (a strided
+    view), out in the compute type.  ``weight``: [Dv] (one vector for all heads) or [H*Dv]; ``gate_act``: silu or the
+    logistic function."""
     _need_cuda(o_raw, gate, weight, out)
     T = o_raw.shape[0]
     assert o_raw.dtype == gate.dtype == weight.dtype == torch.float32 and gate.stride(1) == 1 and out.stride(1) == 1
-    assert gate.shape == (T, H * Dv) and out.shape == (T, H * Dv) and weight.numel() == Dv
+    assert gate.shape == (T, H * Dv) and out.shape == (T, H * Dv) and weight.numel() in (Dv, H * Dv) and weight.is_contiguous()
+    per_head = Dv if (weight.numel() == H * Dv and H > 1) else 0
     _check("delta_finish", lib().llmi_delta_finish(c_int(_dtype_code(out)), _ptr(o_raw), c_long(o_raw.stride(0)), _ptr(gate),
-                                                   c_long(gate.stride(0)), _ptr(weight), c_float(eps), c_int(H), c_int(Dv),
-                                                   _ptr(ctx.tok_seq), _ptr(out), c_long(out.stride(0)), c_int(T), _stream()))
+                                                   c_long(gate.stride(0)), _ptr(weight), c_int(per_head), c_int(gate_act),
+                                                   c_float(eps), c_int(H), c_int(Dv), _ptr(ctx.tok_seq), _ptr(out),
+                                                   c_long(out.stride(0)), c_int(T), _stream()))
+
+
+# ---------------------------------------------------------------------------------------------
+# The delta rule in its general form (csrc/dplr_delta.cu)
+
+def gdelta_prepare(proj: torch.Tensor, H: int, D: int, Dv: int, w2: torch.Tensor, w0, a_bias, ctx, prep: torch.Tensor) -> None:
+    """From the fp32 rows [r | k | v | a | gate | low] (H*D, H*D, H*Dv, H*D, H*Dv, R entries) the recurrence's vectors
+    [w | p | m] (H*D each) into ``prep``: w = exp(-exp(-1/2) sigmoid(w0 + W2 tanh(low))), p = k / |k| per head,
+    m = -sigmoid(a + a_bias) p."""
+    _need_cuda(proj, w2, w0, a_bias, prep)
+    T = proj.shape[0]
+    R = w2.shape[1]
+    assert proj.dtype == prep.dtype == w2.dtype == w0.dtype == a_bias.dtype == torch.float32
+    assert proj.stride(1) == 1 and prep.stride(1) == 1 and proj.shape[1] >= 3 * H * D + 2 * H * Dv + R and prep.shape[1] >= 3 * H * D
+    assert w2.shape == (H * D, R) and w2.is_contiguous() and w0.numel() == H * D and a_bias.numel() == H * D
+    _check("gdelta_prepare", lib().llmi_gdelta_prepare(_ptr(proj), c_long(proj.stride(0)), c_int(H), c_int(D), c_int(Dv), c_int(R),
+                                                       _ptr(w2), _ptr(w0), _ptr(a_bias), _ptr(ctx.tok_seq), _ptr(prep),
+                                                       c_long(prep.stride(0)), c_int(T), _stream()))
+
+
+def dplr_recurrence(proj: torch.Tensor, prep: torch.Tensor, H: int, D: int, Dv: int, state: torch.Tensor, ctx,
+                    o_raw: torch.Tensor, write_state: bool = True) -> None:
+    """Per head S <- diag(w) S + m (p^T S) + k v^T, o = S^T r over the step's tokens of every sequence.  ``proj`` fp32
+    rows with r, k, v at columns 0, H*D, 2*H*D; ``prep`` fp32 rows with w, p, m at 0, H*D, 2*H*D; ``state`` fp32
+    [slots, >= H*D*Dv] (S column by column; read, and updated if ``write_state``); ``o_raw`` fp32 [T, H*Dv]."""
+    _need_cuda(proj, prep, state, o_raw)
+    assert proj.dtype == prep.dtype == state.dtype == o_raw.dtype == torch.float32
+    assert proj.stride(1) == 1 and prep.stride(1) == 1 and o_raw.stride(1) == 1 and state.dim() == 2 and state.stride(1) == 1
+    assert state.shape[1] >= H * D * Dv and o_raw.shape == (proj.shape[0], H * Dv)
+    _check("dplr_recurrence", lib().llmi_dplr_recurrence(
+        _ptr(proj), c_long(proj.stride(0)), _ptr(prep), c_long(prep.stride(0)), c_int(H), c_int(D), c_int(Dv), _ptr(state),
+        c_long(state.stride(0)), _ptr(ctx.seq_q_start), _ptr(ctx.seq_slot), _ptr(o_raw), c_long(o_raw.stride(0)),
+        c_int(ctx.n_seqs), c_int(1 if write_state else 0), _stream()))
 
 
 # ---------------------------------------------------------------------------------------------

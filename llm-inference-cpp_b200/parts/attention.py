@@ -95,3 +95,154 @@ class GQAttention:
         kernels.attention(qkv, attn, g.k[binding.index], g.v[binding.index], ctx, pages, g.page_size,
                           nh, nkv, hd, self.scale, self.window, rt=self.rt, rope=rope)
         return kernels.linear(attn, self.w_o, x, None, kernels.OUT_ADD_F32, then_norm)
+
+
+class _MapsAttention:
+    """What the attention mixers below share: one product for the projections (fp32 rows), ``qkv_prepare`` (norms,
+    rotation, cache append), attention over the call's pages, an optional join of the maps, the output projection.
+
+    Sizes: ``heads`` query heads over ``kv_heads`` key/value heads (query head h reads kv head h // (heads /
+    kv_heads)), ``maps`` score maps per head (query row [head][map][dim]; key heads [kv head][map]), one set of values
+    of size ``vdim`` per kv head.  ``chunk`` > 0: a query at position p sees the keys of its own block of ``chunk``
+    positions only (blocks counted from position 0); ``window`` > 0: the last ``window`` positions only.  A mixer with
+    ``shares_kv`` has no key and value projections: its call reads the cache another call fills (``cache_of`` in the
+    schedule) with its own queries."""
+    maps = 1
+
+    def _sizes(self, p):
+        self.width, self.H, self.G = int(p["width"]), int(p["heads"]), int(p["kv_heads"])
+        self.D, self.Dv = int(p["dim"]), int(p["vdim"])
+        if self.H % self.G:
+            raise ValueError(f"{self.kind}: heads must be a multiple of kv_heads")
+        self.scale, self.eps = float(p["scale"]), float(p["eps"])
+        self.chunk, self.window = int(p.get("chunk", 0)), int(p.get("window", 0))
+        self.shares_kv = bool(p.get("shares_kv", False))
+
+    @classmethod
+    def _declare_projections(cls, p, maps):
+        W, H, G, D, Dv = p["width"], p["heads"], p["kv_heads"], p["dim"], p["vdim"]
+        d = {"q": TensorDecl((H * maps * D, W)), "o": TensorDecl((W, H * Dv))}
+        if not p.get("shares_kv", False):
+            d.update({"k": TensorDecl((G * maps * D, W)), "v": TensorDecl((G * Dv, W))})
+        return d
+
+    def _projections(self, tensors, rt):
+        names = ("q",) if self.shares_kv else ("q", "k", "v")
+        self.w_in = rt.to_compute(torch.cat([tensors[n] for n in names], dim=0))
+        self.w_o = rt.to_compute(tensors["o"])
+
+    def cache_request(self):
+        return KVRequest(self.G * self.maps, self.D, self.window, True, self.G, self.Dv)
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_in, self.w_o))
+
+    @property
+    def takes_padding_rows(self) -> bool:
+        return True          # every kernel skips token rows of no sequence
+
+    # what a subclass adds
+    q_norm_w = k_norm_w = head_scale = None
+    inv_freq, rot_dims = None, 0
+
+    def _attend(self, h, ctx, binding):
+        """-> attention output per map, [T, H*maps*Dv] (fp32 if there are several maps, else the compute type)."""
+        T = h.shape[0]
+        rt, H, G, M, D, Dv = self.rt, self.H, self.G, self.maps, self.D, self.Dv
+        if binding.writes == self.shares_kv:
+            raise ValueError(f"{self.kind}: a layer without key and value projections must read another call's cache, "
+                             f"and only such a layer may")
+        proj = rt.scratch("attn_proj", (T, self.w_in.shape[0]), torch.float32)
+        kernels.linear(h, self.w_in, proj, None, kernels.OUT_STORE_F32)
+        g = binding.group
+        pages = ctx.pages_of(g)
+        k_cache, v_cache = g.k[binding.index], g.v[binding.index]
+        q = rt.scratch("attn_q", (T, H * M * D))
+        kernels.qkv_prepare(proj, H * M, G * M, D, G, Dv, self.q_norm_w, self.k_norm_w, self.eps, self.inv_freq, self.rot_dims,
+                            ctx, pages, g.page_size, k_cache, v_cache, q, has_kv=not self.shares_kv, write_kv=binding.writes)
+        out = rt.scratch("attn_maps" if M > 1 else "attn_out", (T, H * M * Dv), torch.float32 if M > 1 else None)
+        kernels.attention_maps(q, out, k_cache, v_cache, ctx, pages, g.page_size, H, G, M, D, Dv, self.scale, self.head_scale,
+                               self.window, self.chunk, rt=rt)
+        return out
+
+
+@part("mixer", "diff_attention")
+class DiffAttention(_MapsAttention):
+    """Differential attention: two softmax maps per head over the same values, o = a1 - lam * a2 with one number lam
+    for the layer, lam = exp(lq1 . lk1) - exp(lq2 . lk2) + diff; then o / rms(o) over the head's values (no weight)
+    times (1 - diff), and the output projection.  Queries and keys are rotated by position on the first entries of
+    every map (the position part's ``rotary_dim``).
+
+    params: ``width``, ``heads``, ``kv_heads``, ``dim``, ``vdim``, ``scale``, ``diff``, ``eps``, optional ``chunk``,
+    ``window``, ``shares_kv``, ``position`` (a PartSpec of the position family).
+    tensors: ``q`` [heads*2*dim, width], ``k`` [kv_heads*2*dim, width], ``v`` [kv_heads*vdim, width] (k, v absent with
+    ``shares_kv``), ``lq1``, ``lk1``, ``lq2``, ``lk2`` [dim], ``o`` [width, heads*vdim]."""
+    maps = 2
+
+    @classmethod
+    def declare(cls, spec):
+        p = spec.params
+        d = cls._declare_projections(p, 2)
+        d.update({n: TensorDecl((p["dim"],), "bias") for n in ("lq1", "lk1", "lq2", "lk2")})
+        d.update(nested_declare("position", p["position"]))
+        return d
+
+    def __init__(self, spec, tensors, rt, **_):
+        p = spec.params
+        self.rt = rt
+        self._sizes(p)
+        self._projections(tensors, rt)
+        self.diff = float(p["diff"])
+        l = {n: tensors[n].double().cpu() for n in ("lq1", "lk1", "lq2", "lk2")}
+        self.lam = float(torch.exp((l["lq1"] * l["lk1"]).sum()) - torch.exp((l["lq2"] * l["lk2"]).sum()) + self.diff)
+        self.position = nested_build("position", p["position"], tensors, rt)
+        fused = self.position.fused_rotation()
+        if fused is None:
+            raise ValueError("diff_attention: the position part must be a rotation of pairs (or none)")
+        self.inv_freq, self.rot_dims = fused
+        if self.rot_dims > self.D:
+            raise ValueError("diff_attention: the rotated part is larger than a map")
+
+    def forward(self, h, x, ctx, binding, store: bool = False) -> bool:
+        a = self._attend(h, ctx, binding)
+        heads = self.rt.scratch("attn_out", (h.shape[0], self.H * self.Dv))
+        kernels.diff_combine(a, self.lam, self.eps, 1.0 - self.diff, self.H, self.Dv, ctx, heads)
+        kernels.linear(heads, self.w_o, x, None, kernels.OUT_STORE_F32 if store else kernels.OUT_ADD_F32)
+        return False
+
+    stores_output = True
+
+
+@part("mixer", "qk_normed_attention")
+class QKNormedAttention(_MapsAttention):
+    """Attention without positions in its scores: q and k each pass an RMS norm over the WHOLE projected row (all heads
+    at once, a weight per entry) and every head's scores are multiplied by a learned number of its own.
+
+    params: ``width``, ``heads``, ``kv_heads``, ``dim``, ``vdim``, ``scale``, ``eps``, optional ``chunk``, ``window``.
+    tensors: ``q`` [heads*dim, width], ``k`` [kv_heads*dim, width], ``v`` [kv_heads*vdim, width], ``q.norm``
+    [heads*dim], ``k.norm`` [kv_heads*dim], ``temp`` [heads], ``o`` [width, heads*vdim]."""
+
+    @classmethod
+    def declare(cls, spec):
+        p = spec.params
+        d = cls._declare_projections(p, 1)
+        d.update({"q.norm": TensorDecl((p["heads"] * p["dim"],), "norm_scale"),
+                  "k.norm": TensorDecl((p["kv_heads"] * p["dim"],), "norm_scale"),
+                  "temp": TensorDecl((p["heads"],), "norm_scale")})
+        return d
+
+    def __init__(self, spec, tensors, rt, **_):
+        self.rt = rt
+        self._sizes(spec.params)
+        if self.shares_kv:
+            raise ValueError("qk_normed_attention: has key and value projections of its own")
+        self._projections(tensors, rt)
+        self.q_norm_w, self.k_norm_w = rt.to_f32(tensors["q.norm"]), rt.to_f32(tensors["k.norm"])
+        self.head_scale = rt.to_f32(tensors["temp"])
+
+    def forward(self, h, x, ctx, binding, store: bool = False) -> bool:
+        heads = self._attend(h, ctx, binding)
+        kernels.linear(heads, self.w_o, x, None, kernels.OUT_STORE_F32 if store else kernels.OUT_ADD_F32)
+        return False
+
+    stores_output = True

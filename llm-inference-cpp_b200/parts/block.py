@@ -1,5 +1,6 @@
 """Arrangements of a layer.  ``prenorm``: x += mixer(norm(x)); x += ffn(norm(x))
-(include/llmi/model/transformer.hpp:49-52).
+(include/llmi/model/transformer.hpp:49-52); the feed-forward may be absent, and a part in the slot ``mixer_conv``
+(family ``conv``) acts on the mixer's input: x += mixer(conv(norm(x))).
 
 Norm deferral (optional, see :class:`ops.kernels.DeferredNorm`): a mixer or feed-forward whose class sets
 ``defers_norm = True`` accepts a filled deferred norm as its input ``h`` and a keyword ``then_norm`` — a
@@ -22,13 +23,20 @@ def _defers(p) -> bool:
 @part("block", "prenorm")
 class PreNormBlock:
     takes_padding_rows = True       # token rows of no sequence (a step padded to a shape) do no harm: rows are treated alone
-    def __init__(self, mixer_norm, mixer, ffn_norm, ffn):
+    def __init__(self, mixer_norm, mixer, ffn_norm=None, ffn=None, mixer_conv=None):
+        """``ffn_norm`` and ``ffn`` come together or not at all (a layer without a feed-forward); ``mixer_conv`` (a part
+        of the family ``conv``) reshapes what the mixer reads: x += mixer(conv(norm(x)))."""
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("prenorm: a feed-forward comes with its norm, or not at all")
         self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
+        self.mixer_conv = mixer_conv
 
     @property
     def entry_norm(self):
         """The norm this block applies to x first, if whoever updates x before the block may fill its
         deferred form (``forward(..., entry=)``); else None."""
+        if self.mixer_conv is not None:       # the convolution reads the norm's rows themselves
+            return None
         return self.mixer_norm if _defers(self.mixer) and hasattr(self.mixer_norm, "deferred") else None
 
     def forward(self, x, ctx, binding, entry=None, next_norm=None):
@@ -36,6 +44,11 @@ class PreNormBlock:
         that reads x after this block, or None.  Returns that norm's deferred form if the block filled it."""
         T = x.shape[0]
         h = entry if isinstance(entry, kernels.DeferredNorm) else self.mixer_norm.forward(x)
+        if self.mixer_conv is not None:
+            h = self.mixer_conv.forward(h, ctx, binding.more["mixer_conv"])
+        if self.ffn is None:
+            self.mixer.forward(h, x, ctx, binding)
+            return None
         then = None
         if _defers(self.mixer) and _defers(self.ffn) and hasattr(self.ffn_norm, "deferred"):
             then = self.ffn_norm.deferred(T, "deferred_inner")

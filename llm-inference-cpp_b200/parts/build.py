@@ -7,7 +7,7 @@ the parts appear.
 """
 from __future__ import annotations
 
-from . import attention, block, delta, embedding, experts, feedforward, latent, loop, norm, position  # noqa: F401  (register the built-in parts)
+from . import attention, block, conv, delta, embedding, experts, feedforward, latent, loop, norm, position  # noqa: F401  (register the built-in parts)
 from .registry import TensorDecl, get_part
 from .spec import ModelSpec, PartSpec
 
@@ -30,7 +30,7 @@ def expected_tensors(spec: ModelSpec) -> dict:
     for family, ps in _part_specs(spec):
         for local, decl in get_part(family, ps.kind).declare(ps).items():
             name = ps.prefix + local
-            if name in out and tuple(out[name].shape) != tuple(decl.shape):
+            if name in out and tuple(map(repr, out[name].shape)) != tuple(map(repr, decl.shape)):
                 raise ValueError(f"tensor {name} is declared twice with different shapes")
             out[name] = decl
     return out

@@ -18,7 +18,7 @@ import torch
 
 from ..cache.storage import StateRequest
 from ..ops import kernels
-from .registry import TensorDecl, part
+from .registry import FreeDim, TensorDecl, part
 
 
 @part("mixer", "delta")
@@ -79,5 +79,73 @@ class GatedDeltaRule:
                            write_state=binding.writes)
         heads = rt.scratch("attn_out", (T, H * Dv))
         kernels.delta_finish(o_raw, proj[:, self.n_conv + 2 * H:], self.w_norm, self.eps, H, Dv, ctx, heads)
+        kernels.linear(heads, self.w_o, x, None, kernels.OUT_STORE_F32 if store else kernels.OUT_ADD_F32)
+        return False
+
+
+@part("mixer", "general_delta")
+class GeneralDeltaRule:
+    """The delta rule with a decay per key channel and a removal along the unit key.  Per token, from the layer's input
+    h: r, k, v (``heads`` heads of ``dim``) by projections without bias; a decay per head and key channel through a
+    low-rank path, d = exp(-exp(-1/2) * sigmoid(W2 tanh(W1 h) + w0)); a removal rate a = sigmoid(Wa h + a.b); the unit
+    key u = k / sqrt(sum(k^2) + 1e-6).  Per head, both new terms read the old state:
+
+        S <- diag(d) S - (a * u) (uᵀ S) + k vᵀ ;    o = Sᵀ r
+
+    then o / rms(o) per head, times ``norm`` (a weight per entry of all heads), times sigmoid(Wg h), and W_o.  S
+    [heads, dim, dim] lives in the cache's state slab (fp32, column by column, zero at the start); everything behind
+    the projections is fp32 (csrc/dplr_delta.cu).
+
+    params: ``width``, ``heads``, ``dim``, ``eps`` (of the output's RMS norm), optional ``rank`` (the low-rank path's
+    size where random weights are drawn; a file's own size is read from its tensors).
+    tensors: ``r``, ``k``, ``v``, ``a``, ``g`` [heads*dim, width], ``a.b``, ``w0``, ``norm`` [heads*dim], ``w1`` [rank,
+    width], ``w2`` [heads*dim, rank], ``o`` [width, heads*dim]."""
+    stores_output = True
+
+    @classmethod
+    def declare(cls, spec):
+        p = spec.params
+        W, N = p["width"], p["heads"] * p["dim"]
+        R = FreeDim(int(p.get("rank") or max(1, W // 16)))
+        d = {n: TensorDecl((N, W)) for n in ("r", "k", "v", "a", "g")}
+        d.update({"a.b": TensorDecl((N,), "bias"), "w0": TensorDecl((N,), "bias"), "norm": TensorDecl((N,), "norm_scale"),
+                  "w1": TensorDecl((R, W)), "w2": TensorDecl((N, R)), "o": TensorDecl((W, N))})
+        return d
+
+    def __init__(self, spec, tensors, rt, **_):
+        p = spec.params
+        self.rt = rt
+        self.width, self.H, self.D, self.eps = int(p["width"]), int(p["heads"]), int(p["dim"]), float(p["eps"])
+        self.R = int(tensors["w1"].shape[0])
+        if tensors["w2"].shape[1] != self.R:
+            raise ValueError(f"general_delta: w1 has {self.R} rows but w2 has {tensors['w2'].shape[1]} columns")
+        # one product for all projections: rows [r | k | v | a | gate | low-rank path]
+        self.w_in = rt.to_compute(torch.cat([tensors[n] for n in ("r", "k", "v", "a", "g", "w1")], dim=0))
+        self.w2, self.w0, self.a_bias = rt.to_f32(tensors["w2"]), rt.to_f32(tensors["w0"]), rt.to_f32(tensors["a.b"])
+        self.w_norm = rt.to_f32(tensors["norm"])
+        self.w_o = rt.to_compute(tensors["o"])
+
+    def cache_request(self):
+        return StateRequest((self.H * self.D * self.D,), torch.float32)
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_in, self.w_o, self.w2))
+
+    @property
+    def takes_padding_rows(self) -> bool:
+        return True          # every kernel skips token rows and sequences of no slot
+
+    def forward(self, h, x, ctx, binding, store: bool = False) -> bool:
+        T = h.shape[0]
+        rt, H, D = self.rt, self.H, self.D
+        N = H * D
+        proj = rt.scratch("delta_proj", (T, 5 * N + self.R), torch.float32)
+        kernels.linear(h, self.w_in, proj, None, kernels.OUT_STORE_F32)
+        prep = rt.scratch("delta_prep", (T, 3 * N), torch.float32)
+        kernels.gdelta_prepare(proj, H, D, D, self.w2, self.w0, self.a_bias, ctx, prep)
+        o_raw = rt.scratch("delta_o", (T, N), torch.float32)
+        kernels.dplr_recurrence(proj, prep, H, D, D, binding.group.data[binding.index], ctx, o_raw, write_state=binding.writes)
+        heads = rt.scratch("attn_out", (T, N))
+        kernels.delta_finish(o_raw, proj[:, 4 * N:5 * N], self.w_norm, self.eps, H, D, ctx, heads, kernels.GATE_SIGMOID)
         kernels.linear(heads, self.w_o, x, None, kernels.OUT_STORE_F32 if store else kernels.OUT_ADD_F32)
         return False

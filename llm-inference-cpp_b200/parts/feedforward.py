@@ -60,3 +60,45 @@ class SwiGLU:
             kernels.linear(h, self.w_gate_up, gate_up)
             kernels.swiglu(gate_up, act, self.act)
         return kernels.linear(act, self.w_down, x, None, kernels.OUT_STORE_F32 if store else kernels.OUT_ADD_F32, then_norm)
+
+
+@part("ffn", "mlp")
+class DenseMLP:
+    """x += act(h·Wuᵀ + bu)·Wdᵀ + bd: a feed-forward without a gate.  params: ``width``, ``inner``, ``activation`` (``relu2``:
+    the square of relu), optional ``bias`` (default True), optional ``names`` (the local names of the two matrices,
+    default ``up`` and ``down``; a bias is its matrix's name + ``.b``)."""
+    takes_padding_rows = True       # rows are treated alone
+    stores_output = True
+
+    @classmethod
+    def declare(cls, spec):
+        w, f = spec.params["width"], spec.params["inner"]
+        u, d = spec.params.get("names", ("up", "down"))
+        out = {u: TensorDecl((f, w)), d: TensorDecl((w, f))}
+        if spec.params.get("bias", True):
+            out.update({u + ".b": TensorDecl((f,), "bias"), d + ".b": TensorDecl((w,), "bias")})
+        return out
+
+    def __init__(self, spec, tensors, rt, **_):
+        self.rt = rt
+        self.width, self.inner = int(spec.params["width"]), int(spec.params["inner"])
+        u, d = spec.params.get("names", ("up", "down"))
+        activation = spec.params.get("activation", "relu2")
+        if activation not in kernels.PLAIN_ACTIVATIONS:
+            raise ValueError(f"mlp: unknown activation {activation!r} (known: {sorted(kernels.PLAIN_ACTIVATIONS)})")
+        self.act = kernels.PLAIN_ACTIVATIONS[activation]
+        self.w_up, self.w_down = rt.to_compute(tensors[u]), rt.to_compute(tensors[d])
+        bias = spec.params.get("bias", True)
+        self.b_up = rt.to_f32(tensors[u + ".b"]) if bias else None
+        self.b_down = rt.to_f32(tensors[d + ".b"]) if bias else None
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_up, self.w_down))
+
+    def forward(self, h, x, ctx, store: bool = False) -> bool:
+        T = h.shape[0]
+        act = self.rt.scratch("ffn_act", (T, self.inner))
+        kernels.linear(h, self.w_up, act, self.b_up)
+        kernels.activate(act, act, self.act)
+        kernels.linear(act, self.w_down, x, self.b_down, kernels.OUT_STORE_F32 if store else kernels.OUT_ADD_F32)
+        return False

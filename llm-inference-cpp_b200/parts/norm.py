@@ -10,17 +10,18 @@ from .registry import TensorDecl, part
 
 @part("norm", "rms")
 class RMSNorm:
-    """params: ``width``, ``eps``.  tensors: ``weight [width]`` (kept in fp32)."""
+    """params: ``width``, ``eps``, optional ``tensor`` (the weight's local name; default ``weight``).  tensors: the
+    weight [width] (kept in fp32)."""
     takes_padding_rows = True       # token rows of no sequence (a step padded to a shape) do no harm: rows are treated alone
 
     @classmethod
     def declare(cls, spec):
-        return {"weight": TensorDecl((spec.params["width"],), "norm_scale")}
+        return {spec.params.get("tensor", "weight"): TensorDecl((spec.params["width"],), "norm_scale")}
 
     def __init__(self, spec, tensors, rt, **_):
         self.width = int(spec.params["width"])
         self.eps = float(spec.params["eps"])
-        self.weight = rt.to_f32(tensors["weight"])
+        self.weight = rt.to_f32(tensors[spec.params.get("tensor", "weight")])
         self.rt = rt
 
     def forward(self, x, rows=None, scratch_name: str = "norm_out"):

@@ -20,6 +20,10 @@ Families and what the engine calls on their members (``rt`` is the
 ``head``       ``forward(h_rows) -> logits fp32 [rows, vocab]``
 ``pass_entry`` ``forward(x, x0, ctx)``: acts on the stream right before a scheduled call (``ScheduleEntry.before``); ``x0`` is
                the embedding output, kept for the step if the part sets ``needs_embedding_output``
+``conv``       ``cache_request() -> StateRequest | None`` and ``forward(h, ctx, binding) -> h'``: reshapes a sublayer's input
+               over time (a short causal convolution) and keeps the inputs it still needs per sequence; ``binding`` is
+               its own place in the cache (``CacheBinding.more[slot]`` of the call).  Any part of a layer other than the
+               mixer that has ``cache_request`` gets such a place
 
 Every member also has ``declare(spec) -> {local tensor name: TensorDecl}`` (a
 classmethod: what it reads from the weight file under ``spec.prefix``) and is
@@ -49,13 +53,25 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
-FAMILIES = ("norm", "position", "mixer", "ffn", "block", "embedding", "head", "pass_entry")
+FAMILIES = ("norm", "position", "mixer", "ffn", "block", "embedding", "head", "pass_entry", "conv")
 _PARTS: dict[str, dict[str, type]] = {f: {} for f in FAMILIES}
 
 
 @dataclass(frozen=True)
+class FreeDim:
+    """A size that the weight file decides (an inner rank that no configuration key gives): any positive value is
+    accepted, the part reads it from its tensor, and random weights are drawn with ``default``."""
+    default: int
+
+
+def resolved_shape(shape) -> tuple:
+    """A declared shape with every free size at its default (for random weights and parameter counts)."""
+    return tuple(int(d.default) if isinstance(d, FreeDim) else int(d) for d in shape)
+
+
+@dataclass(frozen=True)
 class TensorDecl:
-    shape: tuple
+    shape: tuple                    # sizes; an entry may be a FreeDim
     # "matrix" | "norm_scale" | "bias" | "table": floating tensors (the role says how random weights draw them);
     # "int_table": the only role a file may store as integers
     role: str = "matrix"

@@ -54,6 +54,16 @@ def _shape_and_role(decl) -> tuple:
     return tuple(decl), "matrix"
 
 
+def _is_free(d) -> bool:
+    """A declared size that the file decides (``parts.registry.FreeDim``)."""
+    return hasattr(d, "default") and not isinstance(d, int)
+
+
+def _shape_fits(found, declared) -> bool:
+    found = tuple(found)
+    return len(found) == len(declared) and all((f >= 1) if _is_free(d) else (f == d) for f, d in zip(found, declared))
+
+
 def check_tensors(expected: Mapping[str, tuple], found: Mapping[str, tuple],
                   tolerated: Callable[[str], bool] = lambda n: False, where: str = "model") -> None:
     """``expected``: name → shape, or → a declaration with ``shape`` and ``role``.
@@ -65,8 +75,8 @@ def check_tensors(expected: Mapping[str, tuple], found: Mapping[str, tuple],
             continue
         shape, role = _shape_and_role(decl)
         dt, fshape = found[name]
-        if tuple(fshape) != shape:
-            wrong_shape.append((name, fshape, shape))
+        if not _shape_fits(fshape, shape):
+            wrong_shape.append((name, fshape, tuple("any" if _is_free(d) else d for d in shape)))
         if dt not in (INT_STORAGE if role == "int_table" else FLOAT_STORAGE):
             wrong_dtype.append((name, dt))
     unexpected = [n for n in found if n not in expected and not tolerated(n)]

@@ -17,6 +17,7 @@ import torch
 
 from ..config.registry import parse_config
 from ..parts.build import expected_tensors
+from ..parts.registry import resolved_shape
 from .safetensors_io import write_safetensors
 
 MATRIX_STD = 0.02
@@ -42,7 +43,7 @@ def random_tensor(name: str, shape, role: str, seed: int, device="cpu") -> torch
 
 def random_tensors(spec, seed: int, device="cpu", dtype=torch.float32) -> dict:
     """All tensors a ModelSpec expects, drawn in fp32 and rounded once to ``dtype``."""
-    return {name: random_tensor(name, d.shape, d.role, seed, device).to(dtype)
+    return {name: random_tensor(name, resolved_shape(d.shape), d.role, seed, device).to(dtype)
             for name, d in expected_tensors(spec).items()}
 
 
