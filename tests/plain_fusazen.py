@@ -197,3 +197,11 @@ def forward(cfg, w, tokens, layers_out=None):
         if layers_out is not None:
             layers_out.append(x.copy())
     return (rms_unit(x, eps) * w["final.norm"]) @ w["head"].T
+
+
+def generate_greedy(cfg, w, prompt, n_new):
+    """The ``n_new`` tokens a greedy loop appends to ``prompt`` (first maximum wins), recomputing everything each time."""
+    toks = list(prompt)
+    for _ in range(n_new):
+        toks.append(int(np.argmax(forward(cfg, w, toks)[-1])))
+    return toks[len(prompt):]
