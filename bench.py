@@ -2,8 +2,9 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --workload smollm2-360m|smollm2-135m [--workload-dtypes bfloat16,float32]
-    python bench.py --design garodra [--design-sizes 2048,1024,2048-looped]      (its own JSON line: that design's prefill and
-                                                                                  decode beside the Llama decoder at equal size)
+    python bench.py --design garodra|fusazen [--design-sizes 2048,1024]          (its own JSON line: that design's prefill and
+                                                                                  decode beside the Llama decoder at equal size;
+                                                                                  garodra also has the size 2048-looped)
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 and context 4096 (a
 "step" is one decode step of the whole batch), timed on the device with CUDA events around
@@ -266,12 +267,35 @@ DESIGN_SIZES = {
 }
 
 
+# --design fusazen: the Fusazen design at sizes that resemble a real model's layers, beside the Llama decoder at equal
+# width, depth and feed-forward size.  Eight layers: two-map attention, delta rule, normed attention, delta rule, two-map
+# attention on the first layer's keys and values, delta rule, normed attention, delta rule.  The masks' blocks span the
+# whole context of the decode runs, so that attention reads as many positions as the Llama decoder's.
+def fusazen_config(width, heads, kv_heads, dim, d_heads, ff, vocab, block):
+    diff = {"heads": heads // 2, "kv_heads": kv_heads // 2, "dim": dim, "vdim": 2 * dim, "diff": 0.5, "mask": {"size": block},
+            "rot": {"base": 10000.0, "dims": dim // 2}, "scale": dim ** -0.5}
+    normed = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "mask": {"size": block}, "scale": 1.0 / dim}
+    dlt = {"heads": d_heads, "dim": dim}
+    mlp = {"kind": "dense", "ff": ff}
+    kinds = [("attention", diff), ("general_delta", dlt), ("attention_2", normed), ("general_delta", dlt),
+             ("attention", dict(diff, kv_from=0)), ("general_delta", dlt), ("attention_2", normed), ("general_delta", dlt)]
+    return {"architecture": "Fusazen", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "canon": {"taps": 4}, "layers": [{"type": t, "mixer": m, "mlp": mlp} for t, m in kinds]}
+
+
+FUSAZEN_SIZES = {
+    "2048": (fusazen_config(2048, 32, 8, 64, 32, 8192, 49152, 8192), None),
+    "1024": (fusazen_config(1024, 16, 4, 64, 16, 4096, 49152, 8192), None),
+}
+
+
 class KernelTimes:
     """Device time per entry point of ops.kernels inside real steps (CUDA events around every call; steps run launch
     by launch while this is on, so the figures are shares of a step, not a benchmark of it)."""
     NAMES = ("embed", "rmsnorm", "swiglu", "linear", "rope_store", "attention", "dyt", "dyt_add", "stream_add", "linear_batched",
              "latent_prepare", "latent_q_rotate", "attention_latent", "delta_step", "delta_finish", "moe_route",
-             "moe_experts_streamed", "moe_experts_grouped")
+             "moe_experts_streamed", "moe_experts_grouped", "conv_add", "qkv_prepare", "attention_maps", "diff_combine",
+             "gdelta_prepare", "dplr_recurrence", "activate")
 
     def __init__(self):
         self.spans, self.saved = [], {}
@@ -314,17 +338,20 @@ def design_run(name, steps, warmup, batch, context, tokens, sizes):
     import torch
     import llmi_b200 as L
     from llmi_b200 import SequenceStep
-    if name != "garodra":
+    if name not in ("garodra", "fusazen"):
         print(f"bench.py: unknown design {name!r}")
         return 2
+    table = DESIGN_SIZES if name == "garodra" else FUSAZEN_SIZES
     pk, pk_kind = peaks()
     out = {"design": name, "impl": "ours", "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids, random cache contents)",
            "batch": batch, "context": context, "prefill_tokens": tokens, "steps": steps, "warmup": warmup, "peaks": pk_kind,
            "sizes": {}}
     for size in sizes:
-        g_cfg, l_cfg = DESIGN_SIZES[size]
+        g_cfg, l_cfg = table[size]
+        if l_cfg is None:
+            l_cfg = DESIGN_SIZES[size][1]
         row = {}
-        for label, cfg in (("garodra", g_cfg), ("llama", l_cfg)):
+        for label, cfg in ((name, g_cfg), ("llama", l_cfg)):
             model = L.random_model(cfg, seed=0, dtype="bfloat16", on_device=True)
             pre_ms = prefill_run(model, tokens, iters=3)
             ms, launches, _, _, cache_bytes = decode_run(model, batch, context, steps, warmup)
@@ -381,7 +408,7 @@ def main():
     ap.add_argument("--kv-heads", type=int, default=None,
                     help="with --only: another number of key/value heads (grouped queries), to profile their kernels")
     ap.add_argument("--design", default=None,
-                    help="'garodra': that design's prefill and decode throughput at layer sizes of a real model, beside the "
+                    help="'garodra' or 'fusazen': that design's prefill and decode throughput at layer sizes of a real model, beside the "
                          "Llama decoder at equal size (its own JSON line; the default workload is untouched)")
     ap.add_argument("--design-sizes", default="2048,1024", help="with --design: which of " + ", ".join(sorted(DESIGN_SIZES)))
     args = ap.parse_args()

@@ -66,14 +66,6 @@ __device__ __forceinline__ float flex_dot<float>(const float* __restrict__ q, co
   return acc;
 }
 
-// The first key a query at `pos` sees.
-__device__ __forceinline__ int first_visible(int pos, int window, int chunk) {
-  int lo = 0;
-  if (window > 0 && pos - window + 1 > lo) lo = pos - window + 1;
-  if (chunk > 0 && (pos / chunk) * chunk > lo) lo = (pos / chunk) * chunk;
-  return lo;
-}
-
 // NJ = ceil(dv / 32): output elements per lane.  OutT: the compute type, or float.
 template <typename T, typename OutT, int NJ>
 __global__ void __launch_bounds__(FLEX_WARPS * 32)

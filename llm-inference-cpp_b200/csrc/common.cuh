@@ -77,6 +77,17 @@ __device__ __forceinline__ float rot_hi(float a, float b, float c, float s) { re
 // Callers may ask for mode 4: the gated epilogue of OUT_SWIGLU with the tanh form of GELU as the gate's activation
 // (the launchers turn it into OUT_SWIGLU with `act` = 1).
 constexpr int OUT_GEGLU_REQUEST = 4;
+// and mode 5: a plain store (bias added) through the square of relu (the launchers turn it into OUT_STORE with `act` = 2).
+constexpr int OUT_RELU2_REQUEST = 5;
+constexpr int ACT_STORE_RELU2 = 2;
+// What a storing epilogue writes for the value v (bias added): v, or relu(v)^2 when `act` says so.
+__device__ __forceinline__ float stored_value(float v, int act) {
+  if (act == ACT_STORE_RELU2) {
+    v = fmaxf(v, 0.f);
+    return v * v;
+  }
+  return v;
+}
 
 // act(gate) * up of the gated epilogues.  act 0: silu; 1: 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).  The
 // result is rounded to bf16: the fast exponential and divide suffice (tanh(z) = 1 - 2 / (1 + e^(2z))).

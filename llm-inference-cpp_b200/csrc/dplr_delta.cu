@@ -21,14 +21,28 @@ namespace llmi {
 
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
 
+// dst = tanh(src) row by row (the input of the low-rank path's second product).
+template <typename T>
+__global__ void __launch_bounds__(256)
+tanh_rows_kernel(const float* __restrict__ src, long ld, T* __restrict__ dst, int R, long total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long t = i / R;
+    dst[i] = from_f32<T>(tanhf(src[t * ld + (i - t * R)]));
+  }
+}
+
 // `proj`, one fp32 row per token:  [ r (H*D) | k (H*D) | v (H*Dv) | a (H*D) | gate (H*Dv) | low (R) ].
 // `prep`, one fp32 row per token:  [ w (H*D) | p (H*D) | m (H*D) ]:
-//   w = exp(-exp(-1/2) * sigmoid(w0 + W2 tanh(low)))   (W2 [H*D, R] fp32)
+//   w = exp(-exp(-1/2) * sigmoid(w0 + W2 tanh(low)))   (W2 as w2t [R, H*D] fp32: neighbouring threads read neighbours)
 //   p = k / sqrt(sum_head(k^2) + 1e-6),   m = -sigmoid(a + a_bias) * p
+// With `z` (fp32 [T, ldz], the product W2 tanh(low) made by a matrix product beforehand: the way of a step of many
+// tokens) the kernel adds w0 to it instead of walking the R entries itself.
 __global__ void __launch_bounds__(128)
-gdelta_prepare_kernel(const float* __restrict__ proj, long ld, int H, int D, int Dv, int R, const float* __restrict__ w2,
-                      const float* __restrict__ w0, const float* __restrict__ a_bias, const int32_t* __restrict__ tok_seq,
-                      float* __restrict__ prep, long ldp) {
+gdelta_prepare_kernel(const float* __restrict__ proj, long ld, int H, int D, int Dv, int R, const float* __restrict__ w2t,
+                      const float* __restrict__ z_all, long ldz, const float* __restrict__ w0,
+                      const float* __restrict__ a_bias, const int32_t* __restrict__ tok_seq, float* __restrict__ prep, long ldp) {
   extern __shared__ float low_s[];                       // tanh of the low-rank path's R entries
   __shared__ float scratch[32];
   pdl_launch_dependents();
@@ -38,7 +52,8 @@ gdelta_prepare_kernel(const float* __restrict__ proj, long ld, int H, int D, int
   const int HD = H * D;
   const float* row = proj + (size_t)t * ld;
   const float* low = row + 3 * (size_t)HD + 2 * (size_t)H * Dv;
-  for (int j = threadIdx.x; j < R; j += blockDim.x) low_s[j] = tanhf(low[j]);
+  if (!z_all)
+    for (int j = threadIdx.x; j < R; j += blockDim.x) low_s[j] = tanhf(low[j]);
   const float* k = row + HD + (size_t)h * D;
   float ss = 0.f;
   for (int d = threadIdx.x; d < D; d += blockDim.x) ss = fmaf(k[d], k[d], ss);
@@ -49,8 +64,11 @@ gdelta_prepare_kernel(const float* __restrict__ proj, long ld, int H, int D, int
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     const int c = h * D + d;
     float z = w0[c];
-    const float* wr = w2 + (size_t)c * R;
-    for (int j = 0; j < R; ++j) z = fmaf(wr[j], low_s[j], z);
+    if (z_all) {
+      z += z_all[(size_t)t * ldz + c];
+    } else {
+      for (int j = 0; j < R; ++j) z = fmaf(w2t[(size_t)j * HD + c], low_s[j], z);
+    }
     const float u = k[d] * inv;
     out[d] = expf(-0.6065306597126334f * sigmoid_f(z));
     out[HD + d] = u;
@@ -268,13 +286,27 @@ int launch_dplr_quad(const float* proj, long ld, const float* prep, long ldp, in
 
 using namespace llmi;
 
-LLMI_EXPORT int llmi_gdelta_prepare(const float* proj, long ld, int H, int D, int Dv, int R, const float* w2, const float* w0,
-                                    const float* a_bias, const int32_t* tok_seq, float* prep, long ldp, int n_tokens,
-                                    cudaStream_t stream) {
+// w2t: W2 transposed, fp32 [R, H*D]; z (optional): fp32 [T, ldz] = tanh(low) W2ᵀ made beforehand.
+LLMI_EXPORT int llmi_gdelta_prepare(const float* proj, long ld, int H, int D, int Dv, int R, const float* w2t, const float* z,
+                                    long ldz, const float* w0, const float* a_bias, const int32_t* tok_seq, float* prep, long ldp,
+                                    int n_tokens, cudaStream_t stream) {
   if (n_tokens <= 0 || H <= 0 || H > 65535 || D <= 0 || Dv <= 0 || R <= 0 || R > 8192) return LLMI_ERR_BAD_SIZE;
   const int threads = D > 64 ? 128 : (D > 32 ? 64 : 32);
   return launch_pdl(PDL_SMALL, gdelta_prepare_kernel, dim3(n_tokens, H), dim3(threads), (size_t)R * sizeof(float), stream, proj, ld,
-                    H, D, Dv, R, w2, w0, a_bias, tok_seq, prep, ldp);
+                    H, D, Dv, R, w2t, z, ldz, w0, a_bias, tok_seq, prep, ldp);
+}
+
+// dst [T, R] (type `dtype`, contiguous) = tanh(src[:, :R]); src fp32 rows of pitch ld.
+LLMI_EXPORT int llmi_tanh_rows(int dtype, const float* src, long ld, void* dst, int n_rows, int R, cudaStream_t stream) {
+  if (n_rows <= 0 || R <= 0) return LLMI_ERR_BAD_SIZE;
+  const long total = (long)n_rows * R;
+  const long want = (total + 255) / 256, most = (long)sm_count() * 16;
+  const unsigned blocks = (unsigned)(want < most ? want : most);
+  if (dtype == LLMI_DTYPE_F32)
+    return launch_pdl(PDL_SMALL, tanh_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, src, ld, (float*)dst, R, total);
+  if (dtype == LLMI_DTYPE_BF16)
+    return launch_pdl(PDL_SMALL, tanh_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, src, ld, (__nv_bfloat16*)dst, R, total);
+  return LLMI_ERR_BAD_DTYPE;
 }
 
 // proj fp32 [T, ld]: r at column 0, k at H*D, v at 2*H*D; prep fp32 [T, ldp]: w at 0, p at H*D, m at 2*H*D;

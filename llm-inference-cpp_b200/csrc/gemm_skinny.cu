@@ -62,7 +62,7 @@ struct SkinnyParams {
   const float* in_ss;         // [in_tiles, SK_SS_STRIDE] as written by the product before
   int in_tiles;
   float in_eps;
-  int act;                    // the gate's activation in mode SK_SWIGLU (see gated_value)
+  int act;                    // the gate's activation in mode SK_SWIGLU (see gated_value); in mode SK_STORE 2: relu(v)^2 is stored
 };
 
 // One copy fetches [4 k slices][rows][64 k]: the matrix is seen as a 3-D tensor (k within a slice, row, slice).
@@ -266,7 +266,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         if (live) {
           if (p.bias) v += p.bias[m];
           const size_t o = (size_t)tok * p.ldo + m;
-          if (p.mode == SK_STORE) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
+          if (p.mode == SK_STORE) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(stored_value(v, p.act));
           else if (p.mode == SK_STORE_F32) ((float*)p.out)[o] = v;
           else {
             xn = old[r] + v;
@@ -349,9 +349,10 @@ LLMI_EXPORT int llmi_gemm_skinny(const void* x, long ldx, const void* w, long ld
                                  float* emit_ss, const float* in_ss, int in_tiles, float in_eps, int* error_flag,
                                  cudaStream_t stream) {
   if (n_tok <= 0 || n_tok > 64 || m_out <= 0 || k <= 0) return LLMI_ERR_BAD_SIZE;
-  if (mode < 0 || mode > OUT_GEGLU_REQUEST) return LLMI_ERR_UNSUPPORTED;
-  const int act = mode == OUT_GEGLU_REQUEST ? 1 : 0;
+  if (mode < 0 || mode > OUT_RELU2_REQUEST) return LLMI_ERR_UNSUPPORTED;
+  const int act = mode == OUT_GEGLU_REQUEST ? 1 : (mode == OUT_RELU2_REQUEST ? ACT_STORE_RELU2 : 0);
   if (mode == OUT_GEGLU_REQUEST) mode = SK_SWIGLU;
+  if (mode == OUT_RELU2_REQUEST) mode = SK_STORE;
   if (mode == SK_SWIGLU && ((m_out & 1) || bias)) return LLMI_ERR_UNSUPPORTED;
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || (ldx & 7) || (ldw & 7)) return LLMI_ERR_ALIGN;
   if (k % 64) return LLMI_ERR_UNSUPPORTED;   // the 3-D view of the matrices needs whole 64-wide k slices

@@ -474,7 +474,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           } else if (p.mode == OUT_STORE) {
             __nv_bfloat16* o = (__nv_bfloat16*)bufp + row_in_cta;
 #pragma unroll
-            for (int c = 0; c < 16; ++c) o[c * TC_BM] = __float2bfloat16_rn(v[c] + bias);
+            for (int c = 0; c < 16; ++c) o[c * TC_BM] = __float2bfloat16_rn(stored_value(v[c] + bias, p.act));
           } else {
             float* o = (float*)bufp + row_in_cta;
 #pragma unroll
@@ -713,7 +713,7 @@ __device__ __forceinline__ void wide_way_out(const TcParams& p, const CUtensorMa
     if (p.mode == OUT_STORE) {
       __nv_bfloat16* o = (__nv_bfloat16*)stg + (size_t)(cg * CPT) * RP + row;
 #pragma unroll
-      for (int c = 0; c < CPT; ++c) o[c * RP] = __float2bfloat16_rn(v[c] + b);
+      for (int c = 0; c < CPT; ++c) o[c * RP] = __float2bfloat16_rn(stored_value(v[c] + b, p.act));
     } else {
       float* o = (float*)stg + (size_t)(cg * CPT) * RP + row;
 #pragma unroll
@@ -1097,9 +1097,10 @@ LLMI_EXPORT int llmi_gemm_tc(const void* x, long ldx, const void* w, long ldw, c
                              int n_tok, int m_out, int k, int mode, float* workspace, long workspace_bytes,
                              int* tickets, int n_tickets, int* error_flag, cudaStream_t stream) {
   if (n_tok <= 0 || m_out <= 0 || k <= 0) return LLMI_ERR_BAD_SIZE;
-  if (mode < 0 || mode > OUT_GEGLU_REQUEST) return LLMI_ERR_UNSUPPORTED;
-  const int act = mode == OUT_GEGLU_REQUEST ? 1 : 0;
+  if (mode < 0 || mode > OUT_RELU2_REQUEST) return LLMI_ERR_UNSUPPORTED;
+  const int act = mode == OUT_GEGLU_REQUEST ? 1 : (mode == OUT_RELU2_REQUEST ? ACT_STORE_RELU2 : 0);
   if (mode == OUT_GEGLU_REQUEST) mode = OUT_SWIGLU;
+  if (mode == OUT_RELU2_REQUEST) mode = OUT_STORE;
   if (mode == OUT_SWIGLU && ((m_out & 1) || bias)) return LLMI_ERR_UNSUPPORTED;
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || (ldx & 7) || (ldw & 7)) return LLMI_ERR_ALIGN;
   const int bn = tc_bn(n_tok, m_out);

@@ -44,6 +44,63 @@ conv_add_kernel(const T* __restrict__ h, long ldh, const float* __restrict__ w, 
   y[(size_t)t * ldy + c] = from_f32<T>(own + acc);
 }
 
+// The same for bf16 rows whose channels come in whole groups of eight (16-byte accesses): one thread per (token, eight
+// channels); the sums and their order are those of the kernel above.
+__global__ void __launch_bounds__(128)
+conv_add_vec8_kernel(const __nv_bfloat16* __restrict__ h, long ldh, const float* __restrict__ w, const float* __restrict__ carry_all,
+                     long carry_stride, const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ tok_pos,
+                     const int32_t* __restrict__ seq_q_start, const int32_t* __restrict__ seq_slot, __nv_bfloat16* __restrict__ y,
+                     long ldy, int C, int K) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (c >= C) return;
+  const int seq = tok_seq[t];
+  if (seq < 0) {
+    *reinterpret_cast<uint4*>(y + (size_t)t * ldy + c) = make_uint4(0u, 0u, 0u, 0u);
+    return;
+  }
+  const int slot = seq_slot[seq];
+  const int pos = tok_pos[t], r0 = seq_q_start[seq];
+  const int p0 = pos - (t - r0);
+  const float* carry = carry_all + (size_t)(slot < 0 ? 0 : slot) * carry_stride;
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  for (int j = 0; j < K; ++j) {
+    const int p = pos - (K - 1) + j;
+    if (p < 0) continue;
+    float x[8];
+    if (p >= p0) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(h + (size_t)(r0 + (p - p0)) * ldh + c);
+      const __nv_bfloat162* pr = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(pr[e]);
+        x[2 * e] = f.x;
+        x[2 * e + 1] = f.y;
+      }
+    } else {
+      const float* cr = carry + (size_t)(p - (p0 - (K - 1))) * C + c;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] = cr[e];
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = fmaf(x[e], w[(size_t)(c + e) * K + j], acc[e]);
+  }
+  const uint4 raw = *reinterpret_cast<const uint4*>(h + (size_t)t * ldh + c);
+  const __nv_bfloat162* pr = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  uint4 outv;
+  __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&outv);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 f = __bfloat1622float2(pr[e]);
+    po[e] = __floats2bfloat162_rn(f.x + acc[2 * e], f.y + acc[2 * e + 1]);
+  }
+  *reinterpret_cast<uint4*>(y + (size_t)t * ldy + c) = outv;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 conv_carry_kernel(const T* __restrict__ h, long ldh, float* __restrict__ carry_all, long carry_stride,
@@ -82,9 +139,16 @@ LLMI_EXPORT int llmi_conv_add(int dtype, const void* h, long ldh, const float* w
   if (dtype == LLMI_DTYPE_F32)
     return launch_pdl(PDL_SMALL, conv_add_kernel<float>, grid, dim3(128), 0, stream, (const float*)h, ldh, w, carry, carry_stride,
                       tok_seq, tok_pos, seq_q_start, seq_slot, (float*)y, ldy, C, K);
-  if (dtype == LLMI_DTYPE_BF16)
+  if (dtype == LLMI_DTYPE_BF16) {
+    if (C % 8 == 0 && ldh % 8 == 0 && ldy % 8 == 0 && !((uintptr_t)h & 15) && !((uintptr_t)y & 15)) {
+      const int threads = C / 8 >= 128 ? 128 : ((C / 8 + 31) / 32) * 32;
+      return launch_pdl(PDL_SMALL, conv_add_vec8_kernel, dim3(n_tokens, (C / 8 + threads - 1) / threads), dim3(threads), 0, stream,
+                        (const __nv_bfloat16*)h, ldh, w, carry, carry_stride, tok_seq, tok_pos, seq_q_start, seq_slot,
+                        (__nv_bfloat16*)y, ldy, C, K);
+    }
     return launch_pdl(PDL_SMALL, conv_add_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)h, ldh, w, carry,
                       carry_stride, tok_seq, tok_pos, seq_q_start, seq_slot, (__nv_bfloat16*)y, ldy, C, K);
+  }
   return LLMI_ERR_BAD_DTYPE;
 }
 

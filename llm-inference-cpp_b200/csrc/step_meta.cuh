@@ -26,4 +26,13 @@ __device__ __forceinline__ size_t kv_row_offset(const PagedKV& c, int seq, int p
   return (((size_t)page * c.n_kv_heads + kv_head) * c.page_size + (pos % c.page_size)) * c.head_dim;
 }
 
+// The first key a query at `pos` sees under a window of the last `window` positions (0: none) and a mask of blocks of
+// `chunk` positions counted from position 0 of the sequence (0: none).
+__host__ __device__ __forceinline__ int first_visible(int pos, int window, int chunk) {
+  int lo = 0;
+  if (window > 0 && pos - window + 1 > lo) lo = pos - window + 1;
+  if (chunk > 0 && (pos / chunk) * chunk > lo) lo = (pos / chunk) * chunk;
+  return lo;
+}
+
 }  // namespace llmi

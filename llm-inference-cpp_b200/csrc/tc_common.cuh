@@ -67,7 +67,7 @@ struct TcParams {
   float* workspace;         // [splits][tiles][BN][128] fp32 when splits > 1
   int* tickets;             // [tiles], zero before and after the launch
   int* error_flag;
-  int act;                  // the gate's activation in mode OUT_SWIGLU (see gated_value)
+  int act;                  // the gate's activation in mode OUT_SWIGLU (see gated_value); in mode OUT_STORE 2: relu(v)^2 is stored
 };
 
 // The epilogue of one thread: v holds 16 consecutive tokens (n_base..) of out feature m.  Called by all
@@ -108,7 +108,7 @@ __device__ __forceinline__ void tc_epilogue_store(const TcParams& p, float* v, i
     if (c >= n_valid) break;
     const float val = v[c] + b;
     const size_t idx = (size_t)(n_base + c) * p.ldo + m;
-    if (p.mode == OUT_STORE) ((__nv_bfloat16*)p.out)[idx] = __float2bfloat16_rn(val);
+    if (p.mode == OUT_STORE) ((__nv_bfloat16*)p.out)[idx] = __float2bfloat16_rn(stored_value(val, p.act));
     else ((float*)p.out)[idx] = val;
   }
 }

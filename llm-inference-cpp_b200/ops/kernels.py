@@ -21,7 +21,9 @@ OUT_STORE_F32 = 1    # y (fp32) = x·Wᵀ
 OUT_ADD_F32 = 2      # y (fp32) += x·Wᵀ
 OUT_SWIGLU = 3       # y (compute type) = silu(gate)·up, W's rows alternating gate and up rows (tensor-core kernel only)
 OUT_GEGLU = 4        # the same with the tanh form of GELU as the gate's activation
+OUT_RELU2 = 5        # y (compute type) = relu(x·Wᵀ + bias)², the activation finished in the product's epilogue
 _GATED = (OUT_SWIGLU, OUT_GEGLU)
+_STORES = (OUT_STORE, OUT_RELU2)      # the modes whose output has the compute type and the weight's row count
 
 _ERRORS = {
     -1: "unsupported element type",
@@ -157,11 +159,12 @@ def lib():
                      "llmi_delta_conv_carry", "llmi_delta_recurrence", "llmi_delta_finish", "llmi_moe_route", "llmi_moe_up",
                      "llmi_moe_down", "llmi_moe_grouped", "llmi_linear_heads_mma", "llmi_attention_latent_mma", "llmi_attention_latent_mma_supported",
                      "llmi_conv_add", "llmi_conv_carry", "llmi_qkv_prepare", "llmi_attention_flex", "llmi_diff_combine",
-                     "llmi_gdelta_prepare", "llmi_dplr_recurrence", "llmi_activate"):
+                     "llmi_gdelta_prepare", "llmi_dplr_recurrence", "llmi_activate", "llmi_attention_maps_mma", "llmi_attention_maps_mma_supported", "llmi_tanh_rows"):
             getattr(l, name).restype = c_int
         l.llmi_gemm_tc_workspace.restype = c_long
         l.llmi_delta_state_floats.restype = c_long
         l.llmi_attention_latent_mma_workspace.restype = c_long
+        l.llmi_attention_maps_mma_workspace.restype = c_long
         l.llmi_moe_group_ints.restype = c_long
         l.llmi_attention_decode_workspace.restype = c_long
         # The launchers of a prompt's step are called a few hundred times per step from Python: with their argument
@@ -286,7 +289,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Ten
     N = w.shape[0]
     assert w.shape[1] == K and out.shape == (M, N // 2 if mode in _GATED else N)
     assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
-    assert out.dtype == (torch.bfloat16 if mode in (OUT_STORE, *_GATED) else torch.float32)
+    assert out.dtype == (torch.bfloat16 if mode in (*_STORES, *_GATED) else torch.float32)
     if bias is not None:
         assert bias.dtype == torch.float32 and bias.numel() == N
     sc = tc_scratch(x.device)
@@ -333,7 +336,7 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch
     N = w.shape[0]
     assert w.shape[1] == K and out.shape == (M, N // 2 if mode in _GATED else N)
     assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
-    assert out.dtype == (torch.bfloat16 if mode in (OUT_STORE, *_GATED) else torch.float32)
+    assert out.dtype == (torch.bfloat16 if mode in (*_STORES, *_GATED) else torch.float32)
     if bias is not None:
         assert bias.dtype == torch.float32 and bias.numel() == N
     if then_norm is not None:
@@ -414,6 +417,10 @@ def linear(x, w, out, bias=None, mode: int = OUT_STORE, then_norm: DeferredNorm 
         if x.source is None:
             raise KernelError("a deferred norm that no product has filled")
         rmsnorm(x.source, x.weight, x.h, x.eps)
+    if mode == OUT_RELU2:                # the fp32 FMA product has no activation in its epilogue: two steps
+        linear_simt(xin, w, out, bias, OUT_STORE)
+        activate(out, out, ACT_RELU2)
+        return False
     linear_simt(xin, w, out, bias, mode)
     return False
 
@@ -878,10 +885,50 @@ def attention_flex(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, se
 
 def attention_maps(q, out, k_cache, v_cache, ctx, seq_pages, page_size: int, n_heads: int, n_kv_heads: int, maps: int,
                    dk: int, dv: int, scale: float, head_scale=None, window: int = 0, chunk: int = 0, rt=None) -> None:
-    """The attention of a step in its general form (arguments as :func:`attention_flex`): the kernel that takes the
-    step's sizes and type."""
+    """The attention of a step in its general form (arguments as :func:`attention_flex`): bf16 sizes that the
+    tensor-core kernel takes go there — prompts as blocks of 64 query rows, steps of single tokens cut over the
+    positions (``rt`` lends the workspace of the cuts) —, everything else, and the 32-bit path, to the generic kernel."""
+    if (q.dtype == torch.bfloat16 and rt is not None and _MAPS_ATTENTION == "mma" and not _FORCE_GENERIC_ATTENTION
+            and lib().llmi_attention_maps_mma_supported(c_int(dk), c_int(dv), c_int(n_heads // n_kv_heads), c_int(page_size))
+            and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0 and out.stride(0) % 2 == 0 and out.data_ptr() % 8 == 0):
+        _need_cuda(q, out, k_cache, v_cache, seq_pages, head_scale)
+        T = q.shape[0]
+        S, P = seq_pages.shape
+        assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape == (T, n_heads * maps * dv) and k_cache.is_contiguous()
+        assert v_cache.is_contiguous() and k_cache.shape[-3:] == (n_kv_heads * maps, page_size, dk)
+        assert v_cache.shape[-3:] == (n_kv_heads, page_size, dv) and out.dtype in (torch.bfloat16, torch.float32)
+        prompt = not ctx.decode
+        splits, pps, ws, n_ws = 1, max(P, 1), None, 0
+        if not prompt:
+            splits, pps = maps_attention_plan(S, P, n_kv_heads * maps, window, chunk, page_size)
+            n_ws = int(lib().llmi_attention_maps_mma_workspace(c_int(T), c_int(n_heads), c_int(maps), c_int(dv), c_int(splits)))
+            ws = rt.scratch("attn_maps_partials", (n_ws,), torch.float32)
+        _check("attention_maps_mma", lib().llmi_attention_maps_mma(
+            _ptr(q), c_long(q.stride(0)), _ptr(out), c_long(out.stride(0)), c_int(1 if out.dtype == torch.float32 else 0),
+            _ptr(k_cache), _ptr(v_cache), _ptr(ctx.tok_seq), _ptr(ctx.tok_pos), _ptr(seq_pages), c_int(seq_pages.stride(0)),
+            _ptr(ctx.seq_q_start), _ptr(ctx.seq_kv_len), c_int(T), c_int(S), c_int(n_heads), c_int(n_kv_heads), c_int(maps), c_int(dk),
+            c_int(dv), c_float(scale), _ptr(head_scale), c_int(window), c_int(chunk), c_int(1 if prompt else 0),
+            c_int(T // 64 + S), c_int(splits), c_int(pps), _ptr(ws), c_long(n_ws), _stream()))
+        return
     attention_flex(q, out, k_cache, v_cache, ctx, seq_pages, page_size, n_heads, n_kv_heads, maps, dk, dv, scale, head_scale,
                    window, chunk)
+
+
+_MAPS_ATTENTION = os.environ.get("LLMI_MAPS_ATTENTION", "mma")      # "generic": the fp32-arithmetic kernel for everything
+_MAPS_BLOCKS_PER_SM = int(os.environ.get("LLMI_MAPS_BLOCKS_PER_SM", "2"))
+
+
+def maps_attention_plan(n_seqs: int, n_pages: int, kv_head_maps: int, window: int, chunk: int, page_size: int) -> tuple:
+    """(cuts over the positions, pages per cut) of the tensor-core attention for a step of single tokens: cut until
+    about two blocks per SM are at work.  A query sees at most the pages its window or its block of positions spans.
+    Depends on the step's padded shape only, so a recorded step can be replayed."""
+    visible = max(n_pages, 1)
+    for span in (window, chunk):
+        if span > 0:
+            visible = min(visible, -(-span // page_size) + 1)
+    want = max(1, min(visible, 256, -(-_MAPS_BLOCKS_PER_SM * sm_count() // max(1, n_seqs * kv_head_maps))))
+    pps = -(-visible // want)
+    return -(-visible // pps), pps
 
 
 def diff_combine(a: torch.Tensor, lam: float, eps: float, post: float, H: int, dv: int, ctx, out: torch.Tensor) -> None:
@@ -918,6 +965,7 @@ def conv_add(h: torch.Tensor, w: torch.Tensor, carry: torch.Tensor, ctx, out: to
 
 ACT_RELU2 = 0
 PLAIN_ACTIVATIONS = {"relu2": ACT_RELU2}
+PLAIN_ACTIVATION_MODES = {ACT_RELU2: OUT_RELU2}      # activation -> the output mode of the products that finish it in their epilogue
 
 
 def activate(x: torch.Tensor, out: torch.Tensor, act: int = ACT_RELU2) -> None:
@@ -1128,19 +1176,32 @@ def delta_finish(o_raw: torch.Tensor, gate: torch.Tensor, weight, eps: float, H:
 # ---------------------------------------------------------------------------------------------
 # The delta rule in its general form (csrc/dplr_delta.cu)
 
-def gdelta_prepare(proj: torch.Tensor, H: int, D: int, Dv: int, w2: torch.Tensor, w0, a_bias, ctx, prep: torch.Tensor) -> None:
+def gdelta_prepare(proj: torch.Tensor, H: int, D: int, Dv: int, w2t: torch.Tensor, w0, a_bias, ctx, prep: torch.Tensor,
+                   z: torch.Tensor | None = None) -> None:
     """From the fp32 rows [r | k | v | a | gate | low] (H*D, H*D, H*Dv, H*D, H*Dv, R entries) the recurrence's vectors
     [w | p | m] (H*D each) into ``prep``: w = exp(-exp(-1/2) sigmoid(w0 + W2 tanh(low))), p = k / |k| per head,
-    m = -sigmoid(a + a_bias) p."""
-    _need_cuda(proj, w2, w0, a_bias, prep)
+    m = -sigmoid(a + a_bias) p.  ``w2t``: W2 transposed, fp32 [R, H*D]; ``z`` (optional) fp32 [T, H*D]: W2 tanh(low) made
+    by a matrix product beforehand (:func:`tanh_rows`, :func:`linear`)."""
+    _need_cuda(proj, w2t, w0, a_bias, prep, z)
     T = proj.shape[0]
-    R = w2.shape[1]
-    assert proj.dtype == prep.dtype == w2.dtype == w0.dtype == a_bias.dtype == torch.float32
+    R = w2t.shape[0]
+    assert proj.dtype == prep.dtype == w2t.dtype == w0.dtype == a_bias.dtype == torch.float32
     assert proj.stride(1) == 1 and prep.stride(1) == 1 and proj.shape[1] >= 3 * H * D + 2 * H * Dv + R and prep.shape[1] >= 3 * H * D
-    assert w2.shape == (H * D, R) and w2.is_contiguous() and w0.numel() == H * D and a_bias.numel() == H * D
+    assert w2t.shape == (R, H * D) and w2t.is_contiguous() and w0.numel() == H * D and a_bias.numel() == H * D
+    assert z is None or (z.dtype == torch.float32 and z.shape == (T, H * D) and z.stride(1) == 1)
     _check("gdelta_prepare", lib().llmi_gdelta_prepare(_ptr(proj), c_long(proj.stride(0)), c_int(H), c_int(D), c_int(Dv), c_int(R),
-                                                       _ptr(w2), _ptr(w0), _ptr(a_bias), _ptr(ctx.tok_seq), _ptr(prep),
-                                                       c_long(prep.stride(0)), c_int(T), _stream()))
+                                                       _ptr(w2t), _ptr(z), c_long(z.stride(0) if z is not None else 0), _ptr(w0),
+                                                       _ptr(a_bias), _ptr(ctx.tok_seq), _ptr(prep), c_long(prep.stride(0)),
+                                                       c_int(T), _stream()))
+
+
+def tanh_rows(src: torch.Tensor, out: torch.Tensor) -> None:
+    """out [T, R] (contiguous, any compute type) = tanh(src), src an fp32 view [T, R] with strided rows."""
+    _need_cuda(src, out)
+    T, R = out.shape
+    assert src.dtype == torch.float32 and src.shape == (T, R) and src.stride(1) == 1 and out.is_contiguous()
+    _check("tanh_rows", lib().llmi_tanh_rows(c_int(_dtype_code(out)), _ptr(src), c_long(src.stride(0)), _ptr(out), c_int(T), c_int(R),
+                                             _stream()))
 
 
 def dplr_recurrence(proj: torch.Tensor, prep: torch.Tensor, H: int, D: int, Dv: int, state: torch.Tensor, ctx,

@@ -101,6 +101,7 @@ class GeneralDeltaRule:
     tensors: ``r``, ``k``, ``v``, ``a``, ``g`` [heads*dim, width], ``a.b``, ``w0``, ``norm`` [heads*dim], ``w1`` [rank,
     width], ``w2`` [heads*dim, rank], ``o`` [width, heads*dim]."""
     stores_output = True
+    WALK_MAX_TOKENS = 16     # up to here the decay's low-rank path is walked inside the preparing kernel; beyond, a product
 
     @classmethod
     def declare(cls, spec):
@@ -121,7 +122,9 @@ class GeneralDeltaRule:
             raise ValueError(f"general_delta: w1 has {self.R} rows but w2 has {tensors['w2'].shape[1]} columns")
         # one product for all projections: rows [r | k | v | a | gate | low-rank path]
         self.w_in = rt.to_compute(torch.cat([tensors[n] for n in ("r", "k", "v", "a", "g", "w1")], dim=0))
-        self.w2, self.w0, self.a_bias = rt.to_f32(tensors["w2"]), rt.to_f32(tensors["w0"]), rt.to_f32(tensors["a.b"])
+        self.w2t = rt.to_f32(tensors["w2"]).t().contiguous()          # [rank, heads*dim]: for a handful of tokens, walked in the kernel
+        self.w2 = rt.to_compute(tensors["w2"])                        # for many tokens: a product of its own
+        self.w0, self.a_bias = rt.to_f32(tensors["w0"]), rt.to_f32(tensors["a.b"])
         self.w_norm = rt.to_f32(tensors["norm"])
         self.w_o = rt.to_compute(tensors["o"])
 
@@ -129,7 +132,7 @@ class GeneralDeltaRule:
         return StateRequest((self.H * self.D * self.D,), torch.float32)
 
     def weight_bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in (self.w_in, self.w_o, self.w2))
+        return sum(t.numel() * t.element_size() for t in (self.w_in, self.w_o, self.w2t))
 
     @property
     def takes_padding_rows(self) -> bool:
@@ -142,7 +145,13 @@ class GeneralDeltaRule:
         proj = rt.scratch("delta_proj", (T, 5 * N + self.R), torch.float32)
         kernels.linear(h, self.w_in, proj, None, kernels.OUT_STORE_F32)
         prep = rt.scratch("delta_prep", (T, 3 * N), torch.float32)
-        kernels.gdelta_prepare(proj, H, D, D, self.w2, self.w0, self.a_bias, ctx, prep)
+        z = None
+        if T > self.WALK_MAX_TOKENS:
+            low = rt.scratch("delta_low", (T, self.R))
+            kernels.tanh_rows(proj[:, 5 * N:], low)
+            z = rt.scratch("delta_z", (T, N), torch.float32)
+            kernels.linear(low, self.w2, z, None, kernels.OUT_STORE_F32)
+        kernels.gdelta_prepare(proj, H, D, D, self.w2t, self.w0, self.a_bias, ctx, prep, z)
         o_raw = rt.scratch("delta_o", (T, N), torch.float32)
         kernels.dplr_recurrence(proj, prep, H, D, D, binding.group.data[binding.index], ctx, o_raw, write_state=binding.writes)
         heads = rt.scratch("attn_out", (T, N))

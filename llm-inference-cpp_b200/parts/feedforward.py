@@ -98,7 +98,6 @@ class DenseMLP:
     def forward(self, h, x, ctx, store: bool = False) -> bool:
         T = h.shape[0]
         act = self.rt.scratch("ffn_act", (T, self.inner))
-        kernels.linear(h, self.w_up, act, self.b_up)
-        kernels.activate(act, act, self.act)
+        kernels.linear(h, self.w_up, act, self.b_up, kernels.PLAIN_ACTIVATION_MODES[self.act])      # the activation rides on the product
         kernels.linear(act, self.w_down, x, self.b_down, kernels.OUT_STORE_F32 if store else kernels.OUT_ADD_F32)
         return False

@@ -356,7 +356,14 @@ def test_general_delta_recurrence_against_the_plain_loop(H_, D, R):
         ctx = _one_sequence_ctx(n, pos, n == 1)
         rows = tp[pos:pos + n].contiguous()
         prep = torch.empty((n, 3 * N), device=dev)
-        kernels.gdelta_prepare(rows, H_, D, D, torch.tensor(w2, device=dev), torch.tensor(w0, device=dev), torch.tensor(ab, device=dev), ctx, prep)
+        z = None
+        if n > 30:                                       # the decay's low-rank path as a product of its own
+            low = torch.empty((n, R), device=dev)
+            kernels.tanh_rows(rows[:, 5 * N:], low)
+            z = torch.empty((n, N), device=dev)
+            kernels.linear(low, torch.tensor(w2, device=dev), z, None, kernels.OUT_STORE_F32)
+        kernels.gdelta_prepare(rows, H_, D, D, torch.tensor(w2.T.copy(), device=dev), torch.tensor(w0, device=dev),
+                               torch.tensor(ab, device=dev), ctx, prep, z)
         o_raw = torch.empty((n, N), device=dev)
         kernels.dplr_recurrence(rows, prep, H_, D, D, state, ctx, o_raw)
         out = torch.empty((n, N), device=dev)
@@ -389,3 +396,27 @@ def test_difference_of_two_maps_is_taken_in_32_bits():
     assert (got[2] == 0).all()
     keep = seq >= 0
     assert np.abs(got[keep] - ref[keep]).max() < 1e-2
+
+
+@pytest.mark.parametrize("T", [3, 16, 40, 300, 700])
+def test_squared_relu_finished_in_the_product_equals_the_two_step_form(T):
+    """relu(x W^T + b)^2 finished in the product's epilogue against the product followed by the activation kernel, for the
+    weight-streaming and the tcgen05 kernels' ranges of tokens."""
+    import torch
+    from llmi_b200.ops import kernels
+    gen = torch.Generator(device="cuda:0").manual_seed(T)
+    W, F = 128, 320
+    h = (torch.randn(T, W, generator=gen, device="cuda:0") * 1.5).to(torch.bfloat16)
+    up = (torch.randn(F, W, generator=gen, device="cuda:0") * W ** -0.5).to(torch.bfloat16)
+    b = torch.randn(F, generator=gen, device="cuda:0")
+    fused = torch.empty(T, F, dtype=torch.bfloat16, device="cuda:0")
+    kernels.linear(h, up, fused, b, kernels.OUT_RELU2)
+    two = torch.empty(T, F, dtype=torch.bfloat16, device="cuda:0")
+    kernels.linear(h, up, two, b)
+    kernels.activate(two, two, kernels.ACT_RELU2)
+    ref = torch.clamp(h.double() @ up.double().T + b.double(), min=0) ** 2
+    scale = float(ref.abs().max())
+    assert float((fused.double() - ref).abs().max()) < 6e-3 * scale and float((two.double() - ref).abs().max()) < 2e-2 * scale
+    f32 = torch.empty(T, F, dtype=torch.float32, device="cuda:0")
+    kernels.linear(h.float(), up.float(), f32, b, kernels.OUT_RELU2)          # the 32-bit path: two steps inside
+    assert float((f32.double() - ref).abs().max()) < 1e-5 * scale
