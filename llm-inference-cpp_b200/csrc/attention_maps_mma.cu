@@ -9,8 +9,9 @@
 // sequence's newest position arrive as zeros (their weights are zero, and 0 x anything must stay 0).
 //
 // Two forms of one kernel:
-//   prompts        a block is 64 consecutive tokens of one sequence and one (head, map): four warps of 16 rows each,
-//                  every warp multiplies all 64 keys of a page; the result leaves normalised.
+//   prompts        a block is 128 consecutive tokens of one sequence and one (head, map): eight warps of 16 rows each,
+//                  every warp multiplies all 64 keys of a page; the result leaves normalised.  Blocks of later rows
+//                  (longer key ranges) come first in the grid.
 //   single tokens  a block is one (sequence, kv head, map, cut over the positions): its 16 rows are the query heads
 //                  that share the kv head, every warp takes 16 of a page's 64 keys with a running state of its own,
 //                  and leaves (maximum, sum, unnormalised O) per row in a workspace: cuts x 4 parts per (token, head,
@@ -25,7 +26,8 @@
 
 namespace llmi {
 
-constexpr int AM_PAGE = 64, AM_WARPS = 4, AM_PAD = 8;
+constexpr int AM_PAGE = 64, AM_WARPS = 4, AM_PAD = 8;      // AM_WARPS: of the form for single tokens
+constexpr int AM_PROMPT_WARPS = 8, AM_PROMPT_ROWS = 16 * AM_PROMPT_WARPS;
 
 struct MapsArgs {
   const __nv_bfloat16* q;       // [T, heads, maps, dk]
@@ -52,12 +54,12 @@ struct MapsArgs {
 
 // NV = dv / 16.  PROMPT: the form (see above).
 template <int NV, bool PROMPT>
-__global__ void __launch_bounds__(AM_WARPS * 32)
+__global__ void __launch_bounds__((PROMPT ? AM_PROMPT_WARPS : AM_WARPS) * 32)
 attention_maps_mma_kernel(const MapsArgs a) {
   extern __shared__ __align__(16) unsigned char am_smem[];
   pdl_wait();
   pdl_launch_dependents();
-  constexpr int DV = NV * 16, ROWS = PROMPT ? 64 : 16, NT2 = PROMPT ? 4 : 1;     // NT2: groups of 16 keys a warp takes per page
+  constexpr int DV = NV * 16, ROWS = PROMPT ? AM_PROMPT_ROWS : 16, NT2 = PROMPT ? 4 : 1;     // NT2: groups of 16 keys a warp takes per page
   const int dk = a.dk, ldk = dk + AM_PAD, ldv = DV + AM_PAD;
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(am_smem);                // [ROWS][ldk]
   __nv_bfloat16* k_s = q_s + ROWS * ldk;                                          // [2][64][ldk]
@@ -71,14 +73,14 @@ attention_maps_mma_kernel(const MapsArgs a) {
     seq = -1;
     for (int s = 0; s < a.n_seqs; ++s) {
       const int len = a.seq_q_start[s + 1] - a.seq_q_start[s];
-      const int nb = len > 0 ? (len + 63) / 64 : 0;
-      if (blk < nb) { seq = s; break; }
+      const int nb = len > 0 ? (len + ROWS - 1) / ROWS : 0;
+      if (blk < nb) { seq = s; blk = nb - 1 - blk; break; }      // later rows first: they have the longest key ranges
       blk -= nb;
     }
     if (seq < 0) return;
     const int start = a.seq_q_start[seq], len = a.seq_q_start[seq + 1] - start;
-    t0 = start + 64 * blk;
-    n_rows = min(64, len - 64 * blk);
+    t0 = start + ROWS * blk;
+    n_rows = min(ROWS, len - ROWS * blk);
     head0 = blockIdx.y / a.maps;
     mp = blockIdx.y - head0 * a.maps;
     kvh = head0 / group;
@@ -213,7 +215,7 @@ attention_maps_mma_kernel(const MapsArgs a) {
       mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
       mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
       const float m_new = fmaxf(m_run[i], mx[i]);
-      corr[i] = m_new == -INFINITY ? 1.f : exp2f(m_run[i] - m_new);        // a row that has seen no key yet keeps its zeros
+      corr[i] = m_new == -INFINITY ? 1.f : fast_exp2(m_run[i] - m_new);        // a row that has seen no key yet keeps its zeros
       shift[i] = m_new == -INFINITY ? 0.f : m_new;
       m_run[i] = m_new;
     }
@@ -225,7 +227,7 @@ attention_maps_mma_kernel(const MapsArgs a) {
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
           const int j = 2 * c + jj;
-          const __nv_bfloat162 pp = __floats2bfloat162_rn(exp2f(s[j][2 * i] - shift[i]), exp2f(s[j][2 * i + 1] - shift[i]));
+          const __nv_bfloat162 pp = __floats2bfloat162_rn(fast_exp2(s[j][2 * i] - shift[i]), fast_exp2(s[j][2 * i + 1] - shift[i]));
           ps[i] += __low2float(pp) + __high2float(pp);                       // the sum runs over the rounded weights
           pa[c][2 * jj + i] = *reinterpret_cast<const uint32_t*>(&pp);
         }
@@ -328,7 +330,8 @@ int launch_maps_mma(const MapsArgs& a, dim3 grid, size_t smem, cudaStream_t stre
       return LLMI_ERR_BAD_SIZE;
     allowed.here() = smem;
   }
-  return launch_pdl(PDL_ATTENTION, attention_maps_mma_kernel<NV, PROMPT>, grid, dim3(AM_WARPS * 32), smem, stream, a);
+  return launch_pdl(PDL_ATTENTION, attention_maps_mma_kernel<NV, PROMPT>, grid, dim3((PROMPT ? AM_PROMPT_WARPS : AM_WARPS) * 32), smem,
+                    stream, a);
 }
 
 }  // namespace llmi
@@ -346,7 +349,7 @@ LLMI_EXPORT long llmi_attention_maps_mma_workspace(int n_tokens, int n_heads, in
   return (long)n_tokens * n_heads * maps * splits * AM_WARPS * (dv + 2);
 }
 
-// prompt != 0: n_blocks = an upper bound of the sum over sequences of ceil(tokens / 64).  prompt == 0: every sequence
+// prompt != 0: n_blocks = an upper bound of the sum over sequences of ceil(tokens / 128).  prompt == 0: every sequence
 // brings one token; `splits` cuts of `pages_per_split` pages over the visible positions.
 LLMI_EXPORT int llmi_attention_maps_mma(const void* q, long ldq, void* out, long ldo, int out_f32, const void* k_cache,
                                         const void* v_cache, const int32_t* tok_seq, const int32_t* tok_pos,
@@ -367,7 +370,7 @@ LLMI_EXPORT int llmi_attention_maps_mma(const void* q, long ldq, void* out, long
   a.n_seqs = n_seqs; a.H = n_heads; a.G = n_kv_heads; a.maps = maps; a.dk = dk;
   a.scale_log2 = scale * 1.4426950408889634f; a.head_scale = head_scale; a.window = window; a.chunk = chunk;
   a.splits = splits; a.pages_per_split = pages_per_split; a.ws_o = nullptr; a.ws_ml = nullptr;
-  const int rows = prompt ? 64 : 16;
+  const int rows = prompt ? AM_PROMPT_ROWS : 16;
   const size_t smem = ((size_t)(rows + 2 * AM_PAGE) * (dk + AM_PAD) + (size_t)2 * AM_PAGE * (dv + AM_PAD)) * 2;
   dim3 grid;
   if (prompt) {

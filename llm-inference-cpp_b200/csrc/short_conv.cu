@@ -1,5 +1,5 @@
 // A short causal convolution over time on every channel of a step's rows, added to its own input:
-//     y[t, c] = h[t, c] + sum_{j < K} w[c, j] * h[t - (K-1) + j, c]          (zeros before a sequence's start)
+//     y[t, c] = h[t, c] + sum_{j < K} w[j, c] * h[t - (K-1) + j, c]          (zeros before a sequence's start)
 // The K-1 rows ahead of a step's first token come from the sequence's state (`carry`, fp32, [K-1][C] per slot:
 // the inputs at positions p0-(K-1) .. p0-1), which a second kernel brings up to date after the step.  The sum is
 // fp32, taps in the order oldest first, so a position's result does not depend on how its sequence was cut.
@@ -7,6 +7,7 @@
 //   llmi_conv_add     one thread per (token, channel)
 //   llmi_conv_carry   one thread per (sequence, channel): the inputs of the last K-1 positions after this step,
 //                     from the step's own rows or, where the step brought fewer, from what the state held
+//   llmi_norm_conv_token   a step of single tokens: the norm ahead, the convolution and the state's update in one
 #include "common.cuh"
 
 namespace llmi {
@@ -39,7 +40,7 @@ conv_add_kernel(const T* __restrict__ h, long ldh, const float* __restrict__ w, 
     const int p = pos - (K - 1) + j;
     if (p < 0) continue;
     const float x = p >= p0 ? to_f32(h[(size_t)(r0 + (p - p0)) * ldh + c]) : carry[(size_t)(p - (p0 - (K - 1))) * C + c];
-    acc = fmaf(x, w[(size_t)c * K + j], acc);
+    acc = fmaf(x, w[(size_t)j * C + c], acc);
   }
   y[(size_t)t * ldy + c] = from_f32<T>(own + acc);
 }
@@ -86,8 +87,10 @@ conv_add_vec8_kernel(const __nv_bfloat16* __restrict__ h, long ldh, const float*
 #pragma unroll
       for (int e = 0; e < 8; ++e) x[e] = cr[e];
     }
+    const float4 w0 = *reinterpret_cast<const float4*>(w + (size_t)j * C + c), w1 = *reinterpret_cast<const float4*>(w + (size_t)j * C + c + 4);
+    const float we[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] = fmaf(x[e], w[(size_t)(c + e) * K + j], acc[e]);
+    for (int e = 0; e < 8; ++e) acc[e] = fmaf(x[e], we[e], acc[e]);
   }
   const uint4 raw = *reinterpret_cast<const uint4*>(h + (size_t)t * ldh + c);
   const __nv_bfloat162* pr = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -126,11 +129,75 @@ conv_carry_kernel(const T* __restrict__ h, long ldh, float* __restrict__ carry_a
   for (int j = 0; j < K - 1; ++j) carry[(size_t)j * C + c] = keep[j];
 }
 
+// A step in which every sequence brings ONE token: the RMS norm ahead of the convolution, the convolution and the
+// state's update in one kernel, one thread per (token, channel).  h = T(weight * (x * rsqrt(mean(x^2) + eps))) is rounded to the
+// compute type as the norm kernel rounds it, the taps are added oldest first as above, and the thread that owns a
+// channel reads its state entries before it writes them: the results are those of the three kernels.
+template <typename T>
+__global__ void __launch_bounds__(256)
+norm_conv_token_kernel(const float* __restrict__ x, const float* __restrict__ norm_w, float eps, const float* __restrict__ w,
+                       float* carry_all, long carry_stride, const int32_t* __restrict__ tok_seq,
+                       const int32_t* __restrict__ seq_slot, T* __restrict__ y, long ldy, int C, int K, int write_state) {
+  __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;       // my channel; every block of a token sums the whole row itself
+  const int seq = tok_seq[t];
+  const int slot = seq < 0 ? -1 : seq_slot[seq];
+  if (slot < 0) {
+    if (c < C) y[(size_t)t * ldy + c] = from_f32<T>(0.f);
+    return;
+  }
+  const float* xr = x + (size_t)t * C;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < C; i += blockDim.x) ss = fmaf(xr[i], xr[i], ss);
+  ss = block_sum(ss, scratch);
+  if (c >= C) return;
+  const float scale = 1.0f / sqrtf(ss / (float)C + eps);
+  float* carry = carry_all + (size_t)slot * carry_stride;
+  float old[CONV_MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
+    if (j < K - 1) old[j] = carry[(size_t)j * C + c];          // all of my state first: independent loads, and read before written
+  const float h = to_f32(from_f32<T>(norm_w[c] * (xr[c] * scale)));
+  float acc = 0.f;
+#pragma unroll
+  for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
+    if (j < K - 1) acc = fmaf(old[j], w[(size_t)j * C + c], acc);
+  acc = fmaf(h, w[(size_t)(K - 1) * C + c], acc);
+  y[(size_t)t * ldy + c] = from_f32<T>(h + acc);
+  if (write_state && K > 1) {
+#pragma unroll
+    for (int j = 1; j < CONV_MAX_TAPS - 1; ++j)
+      if (j < K - 1) carry[(size_t)(j - 1) * C + c] = old[j];
+    carry[(size_t)(K - 2) * C + c] = h;
+  }
+}
+
 }  // namespace llmi
 
 using namespace llmi;
 
-// y = h + conv(h); h, y [T, C] in the type `dtype`; w fp32 [C, K]; carry fp32 [slots, carry_stride >= (K-1)*C].
+// For a step of single tokens: y [T, C] (type `dtype`) = h + conv(h) with h the RMS norm of the fp32 rows x [T, C]
+// (contiguous), and the state brought up to date.
+LLMI_EXPORT int llmi_norm_conv_token(int dtype, const float* x, const float* norm_w, float eps, const float* w, float* carry,
+                                     long carry_stride, const int32_t* tok_seq, const int32_t* seq_slot, void* y, long ldy,
+                                     int n_tokens, int C, int K, int write_state, cudaStream_t stream) {
+  if (n_tokens <= 0 || C <= 0 || K < 1 || K > CONV_MAX_TAPS) return LLMI_ERR_BAD_SIZE;
+  const int threads = C >= 1024 ? 256 : (C >= 256 ? 128 : 64);
+  const dim3 grid(n_tokens, (C + threads - 1) / threads);
+  if (grid.y > 65535) return LLMI_ERR_BAD_SIZE;
+  if (dtype == LLMI_DTYPE_F32)
+    return launch_pdl(PDL_SMALL, norm_conv_token_kernel<float>, grid, dim3(threads), 0, stream, x, norm_w, eps, w, carry,
+                      carry_stride, tok_seq, seq_slot, (float*)y, ldy, C, K, write_state);
+  if (dtype == LLMI_DTYPE_BF16)
+    return launch_pdl(PDL_SMALL, norm_conv_token_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, x, norm_w, eps, w,
+                      carry, carry_stride, tok_seq, seq_slot, (__nv_bfloat16*)y, ldy, C, K, write_state);
+  return LLMI_ERR_BAD_DTYPE;
+}
+
+// y = h + conv(h); h, y [T, C] in the type `dtype`; w fp32 [K, C] (tap-major); carry fp32 [slots, carry_stride >= (K-1)*C].
 LLMI_EXPORT int llmi_conv_add(int dtype, const void* h, long ldh, const float* w, const float* carry, long carry_stride,
                               const int32_t* tok_seq, const int32_t* tok_pos, const int32_t* seq_q_start,
                               const int32_t* seq_slot, void* y, long ldy, int n_tokens, int C, int K, cudaStream_t stream) {
@@ -140,7 +207,7 @@ LLMI_EXPORT int llmi_conv_add(int dtype, const void* h, long ldh, const float* w
     return launch_pdl(PDL_SMALL, conv_add_kernel<float>, grid, dim3(128), 0, stream, (const float*)h, ldh, w, carry, carry_stride,
                       tok_seq, tok_pos, seq_q_start, seq_slot, (float*)y, ldy, C, K);
   if (dtype == LLMI_DTYPE_BF16) {
-    if (C % 8 == 0 && ldh % 8 == 0 && ldy % 8 == 0 && !((uintptr_t)h & 15) && !((uintptr_t)y & 15)) {
+    if (C % 8 == 0 && ldh % 8 == 0 && ldy % 8 == 0 && !((uintptr_t)h & 15) && !((uintptr_t)y & 15) && !((uintptr_t)w & 15)) {
       const int threads = C / 8 >= 128 ? 128 : ((C / 8 + 31) / 32) * 32;
       return launch_pdl(PDL_SMALL, conv_add_vec8_kernel, dim3(n_tokens, (C / 8 + threads - 1) / threads), dim3(threads), 0, stream,
                         (const __nv_bfloat16*)h, ldh, w, carry, carry_stride, tok_seq, tok_pos, seq_q_start, seq_slot,

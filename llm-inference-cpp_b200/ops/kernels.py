@@ -159,7 +159,7 @@ def lib():
                      "llmi_delta_conv_carry", "llmi_delta_recurrence", "llmi_delta_finish", "llmi_moe_route", "llmi_moe_up",
                      "llmi_moe_down", "llmi_moe_grouped", "llmi_linear_heads_mma", "llmi_attention_latent_mma", "llmi_attention_latent_mma_supported",
                      "llmi_conv_add", "llmi_conv_carry", "llmi_qkv_prepare", "llmi_attention_flex", "llmi_diff_combine",
-                     "llmi_gdelta_prepare", "llmi_dplr_recurrence", "llmi_activate", "llmi_attention_maps_mma", "llmi_attention_maps_mma_supported", "llmi_tanh_rows"):
+                     "llmi_gdelta_prepare", "llmi_dplr_recurrence", "llmi_activate", "llmi_attention_maps_mma", "llmi_attention_maps_mma_supported", "llmi_tanh_rows", "llmi_norm_conv_token"):
             getattr(l, name).restype = c_int
         l.llmi_gemm_tc_workspace.restype = c_long
         l.llmi_delta_state_floats.restype = c_long
@@ -886,7 +886,7 @@ def attention_flex(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, se
 def attention_maps(q, out, k_cache, v_cache, ctx, seq_pages, page_size: int, n_heads: int, n_kv_heads: int, maps: int,
                    dk: int, dv: int, scale: float, head_scale=None, window: int = 0, chunk: int = 0, rt=None) -> None:
     """The attention of a step in its general form (arguments as :func:`attention_flex`): bf16 sizes that the
-    tensor-core kernel takes go there — prompts as blocks of 64 query rows, steps of single tokens cut over the
+    tensor-core kernel takes go there — prompts as blocks of 128 query rows, steps of single tokens cut over the
     positions (``rt`` lends the workspace of the cuts) —, everything else, and the 32-bit path, to the generic kernel."""
     if (q.dtype == torch.bfloat16 and rt is not None and _MAPS_ATTENTION == "mma" and not _FORCE_GENERIC_ATTENTION
             and lib().llmi_attention_maps_mma_supported(c_int(dk), c_int(dv), c_int(n_heads // n_kv_heads), c_int(page_size))
@@ -908,7 +908,7 @@ def attention_maps(q, out, k_cache, v_cache, ctx, seq_pages, page_size: int, n_h
             _ptr(k_cache), _ptr(v_cache), _ptr(ctx.tok_seq), _ptr(ctx.tok_pos), _ptr(seq_pages), c_int(seq_pages.stride(0)),
             _ptr(ctx.seq_q_start), _ptr(ctx.seq_kv_len), c_int(T), c_int(S), c_int(n_heads), c_int(n_kv_heads), c_int(maps), c_int(dk),
             c_int(dv), c_float(scale), _ptr(head_scale), c_int(window), c_int(chunk), c_int(1 if prompt else 0),
-            c_int(T // 64 + S), c_int(splits), c_int(pps), _ptr(ws), c_long(n_ws), _stream()))
+            c_int(T // 128 + S), c_int(splits), c_int(pps), _ptr(ws), c_long(n_ws), _stream()))
         return
     attention_flex(q, out, k_cache, v_cache, ctx, seq_pages, page_size, n_heads, n_kv_heads, maps, dk, dv, scale, head_scale,
                    window, chunk)
@@ -945,13 +945,14 @@ def diff_combine(a: torch.Tensor, lam: float, eps: float, post: float, H: int, d
 # A short convolution over time with a carried state (csrc/short_conv.cu); plain activations
 
 def conv_add(h: torch.Tensor, w: torch.Tensor, carry: torch.Tensor, ctx, out: torch.Tensor, write_state: bool = True) -> None:
-    """out = h + conv(h): per channel a causal convolution over time with ``w`` fp32 [C, K]; the K-1 inputs ahead of a
-    step's first row come from ``carry`` fp32 [slots, >= (K-1)*C], which is then brought up to date."""
+    """out = h + conv(h): per channel a causal convolution over time with the taps ``w`` fp32 [K, C] (tap-major: the
+    channels of a tap lie side by side; the oldest tap first); the K-1 inputs ahead of a step's first row come from
+    ``carry`` fp32 [slots, >= (K-1)*C], which is then brought up to date."""
     _need_cuda(h, w, carry, out)
     T, C = h.shape
-    K = w.shape[1]
+    K = w.shape[0]
     assert h.stride(1) == 1 and out.stride(1) == 1 and out.shape == (T, C) and out.dtype == h.dtype
-    assert w.dtype == torch.float32 and w.shape == (C, K) and w.is_contiguous()
+    assert w.dtype == torch.float32 and w.shape == (K, C) and w.is_contiguous()
     assert carry.dtype == torch.float32 and carry.dim() == 2 and carry.stride(1) == 1 and carry.shape[1] >= (K - 1) * C
     assert out.data_ptr() != h.data_ptr()
     _check("conv_add", lib().llmi_conv_add(c_int(_dtype_code(h)), _ptr(h), c_long(h.stride(0)), _ptr(w), _ptr(carry),
@@ -961,6 +962,23 @@ def conv_add(h: torch.Tensor, w: torch.Tensor, carry: torch.Tensor, ctx, out: to
         _check("conv_carry", lib().llmi_conv_carry(c_int(_dtype_code(h)), _ptr(h), c_long(h.stride(0)), _ptr(carry),
                                                    c_long(carry.stride(0)), _ptr(ctx.seq_q_start), _ptr(ctx.seq_kv_len),
                                                    _ptr(ctx.seq_slot), c_int(ctx.n_seqs), c_int(C), c_int(K), _stream()))
+
+
+def norm_conv_token(x: torch.Tensor, norm_w: torch.Tensor, eps: float, w: torch.Tensor, carry: torch.Tensor, ctx,
+                    out: torch.Tensor, write_state: bool = True) -> None:
+    """For a step in which every sequence brings one token: out = h + conv(h) with h = rmsnorm(x) (rounded to out's type
+    as :func:`rmsnorm` rounds it), and ``carry`` brought up to date — the results of :func:`rmsnorm` + :func:`conv_add`
+    in one kernel.  x fp32 [T, C] contiguous; w fp32 [K, C]."""
+    _need_cuda(x, norm_w, w, carry, out)
+    T, C = x.shape
+    K = w.shape[0]
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.shape == (T, C) and out.stride(1) == 1
+    assert norm_w.dtype == torch.float32 and norm_w.numel() == C and w.dtype == torch.float32 and w.shape == (K, C) and w.is_contiguous()
+    assert carry.dtype == torch.float32 and carry.dim() == 2 and carry.stride(1) == 1 and carry.shape[1] >= (K - 1) * C
+    _check("norm_conv_token", lib().llmi_norm_conv_token(
+        c_int(_dtype_code(out)), _ptr(x), _ptr(norm_w), c_float(eps), _ptr(w), _ptr(carry), c_long(carry.stride(0)),
+        _ptr(ctx.tok_seq), _ptr(ctx.seq_slot), _ptr(out), c_long(out.stride(0)), c_int(T), c_int(C), c_int(K),
+        c_int(1 if write_state else 0), _stream()))
 
 
 ACT_RELU2 = 0

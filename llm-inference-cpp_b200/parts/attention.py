@@ -141,6 +141,14 @@ class _MapsAttention:
     def takes_padding_rows(self) -> bool:
         return True          # every kernel skips token rows of no sequence
 
+    defers_norm = True       # the output projection can fill the norm behind the mixer (``then_norm``); the input is plain rows
+
+    def _project_out(self, heads, x, store, then_norm) -> bool:
+        if store:
+            kernels.linear(heads, self.w_o, x, None, kernels.OUT_STORE_F32)
+            return False
+        return kernels.linear(heads, self.w_o, x, None, kernels.OUT_ADD_F32, then_norm)
+
     # what a subclass adds
     q_norm_w = k_norm_w = head_scale = None
     inv_freq, rot_dims = None, 0
@@ -203,12 +211,11 @@ class DiffAttention(_MapsAttention):
         if self.rot_dims > self.D:
             raise ValueError("diff_attention: the rotated part is larger than a map")
 
-    def forward(self, h, x, ctx, binding, store: bool = False) -> bool:
+    def forward(self, h, x, ctx, binding, store: bool = False, then_norm=None) -> bool:
         a = self._attend(h, ctx, binding)
         heads = self.rt.scratch("attn_out", (h.shape[0], self.H * self.Dv))
         kernels.diff_combine(a, self.lam, self.eps, 1.0 - self.diff, self.H, self.Dv, ctx, heads)
-        kernels.linear(heads, self.w_o, x, None, kernels.OUT_STORE_F32 if store else kernels.OUT_ADD_F32)
-        return False
+        return self._project_out(heads, x, store, then_norm)
 
     stores_output = True
 
@@ -240,9 +247,7 @@ class QKNormedAttention(_MapsAttention):
         self.q_norm_w, self.k_norm_w = rt.to_f32(tensors["q.norm"]), rt.to_f32(tensors["k.norm"])
         self.head_scale = rt.to_f32(tensors["temp"])
 
-    def forward(self, h, x, ctx, binding, store: bool = False) -> bool:
-        heads = self._attend(h, ctx, binding)
-        kernels.linear(heads, self.w_o, x, None, kernels.OUT_STORE_F32 if store else kernels.OUT_ADD_F32)
-        return False
+    def forward(self, h, x, ctx, binding, store: bool = False, then_norm=None) -> bool:
+        return self._project_out(self._attend(h, ctx, binding), x, store, then_norm)
 
     stores_output = True

@@ -43,9 +43,14 @@ class PreNormBlock:
         """``entry``: the filled deferred form of this block's first norm, or None.  ``next_norm``: the norm
         that reads x after this block, or None.  Returns that norm's deferred form if the block filled it."""
         T = x.shape[0]
-        h = entry if isinstance(entry, kernels.DeferredNorm) else self.mixer_norm.forward(x)
+        h = None
         if self.mixer_conv is not None:
-            h = self.mixer_conv.forward(h, ctx, binding.more["mixer_conv"])
+            fused = getattr(self.mixer_conv, "forward_from_stream", None)
+            h = fused(x, self.mixer_norm, ctx, binding.more["mixer_conv"]) if fused is not None else None
+            if h is None:
+                h = self.mixer_conv.forward(self.mixer_norm.forward(x), ctx, binding.more["mixer_conv"])
+        else:
+            h = entry if isinstance(entry, kernels.DeferredNorm) else self.mixer_norm.forward(x)
         if self.ffn is None:
             self.mixer.forward(h, x, ctx, binding)
             return None

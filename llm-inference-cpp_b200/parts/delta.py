@@ -138,7 +138,9 @@ class GeneralDeltaRule:
     def takes_padding_rows(self) -> bool:
         return True          # every kernel skips token rows and sequences of no slot
 
-    def forward(self, h, x, ctx, binding, store: bool = False) -> bool:
+    defers_norm = True       # the output projection can fill the norm behind the mixer (``then_norm``)
+
+    def forward(self, h, x, ctx, binding, store: bool = False, then_norm=None) -> bool:
         T = h.shape[0]
         rt, H, D = self.rt, self.H, self.D
         N = H * D
@@ -156,5 +158,7 @@ class GeneralDeltaRule:
         kernels.dplr_recurrence(proj, prep, H, D, D, binding.group.data[binding.index], ctx, o_raw, write_state=binding.writes)
         heads = rt.scratch("attn_out", (T, N))
         kernels.delta_finish(o_raw, proj[:, 4 * N:5 * N], self.w_norm, self.eps, H, D, ctx, heads, kernels.GATE_SIGMOID)
-        kernels.linear(heads, self.w_o, x, None, kernels.OUT_STORE_F32 if store else kernels.OUT_ADD_F32)
-        return False
+        if store:
+            kernels.linear(heads, self.w_o, x, None, kernels.OUT_STORE_F32)
+            return False
+        return kernels.linear(heads, self.w_o, x, None, kernels.OUT_ADD_F32, then_norm)

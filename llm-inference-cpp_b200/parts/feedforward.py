@@ -95,9 +95,13 @@ class DenseMLP:
     def weight_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.w_up, self.w_down))
 
-    def forward(self, h, x, ctx, store: bool = False) -> bool:
+    defers_norm = True       # takes a deferred norm as its input, and its down projection can fill the next one
+
+    def forward(self, h, x, ctx, then_norm=None, store: bool = False) -> bool:
         T = h.shape[0]
         act = self.rt.scratch("ffn_act", (T, self.inner))
         kernels.linear(h, self.w_up, act, self.b_up, kernels.PLAIN_ACTIVATION_MODES[self.act])      # the activation rides on the product
-        kernels.linear(act, self.w_down, x, self.b_down, kernels.OUT_STORE_F32 if store else kernels.OUT_ADD_F32)
-        return False
+        if store:
+            kernels.linear(act, self.w_down, x, self.b_down, kernels.OUT_STORE_F32)
+            return False
+        return kernels.linear(act, self.w_down, x, self.b_down, kernels.OUT_ADD_F32, then_norm)

@@ -307,7 +307,7 @@ def test_short_convolution_carries_its_inputs_over_every_cut(taps, width, dtype)
     h = torch.tensor(rng.standard_normal((N, width)).astype(np.float32)).to(dt)
     w = rng.standard_normal((width, taps)).astype(np.float32)
     ref = G.time_conv_add(h.float().numpy().astype(np.float64), w.astype(np.float64))
-    tw = torch.tensor(w, device="cuda:0")
+    tw = torch.tensor(w.T.copy(), device="cuda:0")             # the kernel takes the taps tap-major
     cuts = [1, 2, 3, max(1, taps - 1), taps, 30]
     state = torch.full((3, max(taps - 1, 1) * width), float("nan"), device="cuda:0")
     state[0].zero_()
