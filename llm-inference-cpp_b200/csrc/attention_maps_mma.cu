@@ -13,9 +13,10 @@
 //                  every warp multiplies all 64 keys of a page; the result leaves normalised.  Blocks of later rows
 //                  (longer key ranges) come first in the grid.
 //   single tokens  a block is one (sequence, kv head, map, cut over the positions): its 16 rows are the query heads
-//                  that share the kv head, every warp takes 16 of a page's 64 keys with a running state of its own,
-//                  and leaves (maximum, sum, unnormalised O) per row in a workspace: cuts x 4 parts per (token, head,
-//                  map), which a second kernel joins in a fixed order.
+//                  that share the kv head, every warp takes 16 of a page's 64 keys with a running state of its own;
+//                  the four states meet in shared memory in warp order, and the block leaves (maximum, sum,
+//                  unnormalised O) per row in a workspace, one part per cut, which a second kernel joins in a fixed
+//                  order — or the finished row, when the positions are not cut.
 // The order of every addition depends on positions only (pages anchored at multiples of 64, parts by key index), not
 // on the batch; cuts follow the page table's width, which is part of a recorded step's shape.
 #include <math.h>
@@ -48,8 +49,8 @@ struct MapsArgs {
   const float* head_scale;      // [H] or null
   int window, chunk;
   int splits, pages_per_split;  // single tokens
-  float* ws_o;                  // [T * H * maps][splits * 4][dv]
-  float* ws_ml;                 // [T * H * maps][splits * 4][2]
+  float* ws_o;                  // [T * H * maps][splits][dv]
+  float* ws_ml;                 // [T * H * maps][splits][2]
 };
 
 // NV = dv / 16.  PROMPT: the form (see above).
@@ -86,13 +87,21 @@ attention_maps_mma_kernel(const MapsArgs a) {
     kvh = head0 / group;
   } else {
     seq = blockIdx.x;
-    if (a.seq_kv_len[seq] <= 0) return;
     t0 = a.seq_q_start[seq];
     n_rows = 1;
     kvh = blockIdx.y / a.maps;
     mp = blockIdx.y - kvh * a.maps;
     head0 = kvh * group;
     split = blockIdx.z;
+    if (a.seq_kv_len[seq] <= 0 || a.tok_seq[t0] < 0) {
+      if (a.splits == 1)                                        // a sequence of no token: zeros (with cuts, the joining kernel writes them)
+        for (int idx = threadIdx.x; idx < group * (NV * 16); idx += blockDim.x) {
+          const size_t at = (size_t)t0 * a.ldo + ((size_t)(head0 + idx / (NV * 16)) * a.maps + mp) * (NV * 16) + idx % (NV * 16);
+          if (a.out_f32) ((float*)a.out)[at] = 0.f;
+          else ((__nv_bfloat16*)a.out)[at] = __float2bfloat16_rn(0.f);
+        }
+      return;
+    }
   }
   if (a.tok_seq[t0] < 0) return;
   const int newest = a.seq_kv_len[seq] - 1;
@@ -257,8 +266,8 @@ attention_maps_mma_kernel(const MapsArgs a) {
 
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    if (row_pos[i] < 0) continue;
-    if (PROMPT) {
+    if (!PROMPT || row_pos[i] < 0) continue;
+    {
       const int t = t0 + 16 * warp + g + 8 * i;
       const float inv = 1.0f / l_run[i];
       const size_t at = (size_t)t * a.ldo + (size_t)(head0 * a.maps + mp) * DV + 2 * tq;
@@ -267,16 +276,50 @@ attention_maps_mma_kernel(const MapsArgs a) {
         if (a.out_f32) *reinterpret_cast<float2*>((float*)a.out + at + 8 * j) = make_float2(o[j][2 * i] * inv, o[j][2 * i + 1] * inv);
         else *reinterpret_cast<__nv_bfloat162*>((__nv_bfloat16*)a.out + at + 8 * j) = __floats2bfloat162_rn(o[j][2 * i] * inv, o[j][2 * i + 1] * inv);
       }
-    } else {
-      const int parts = a.splits * AM_WARPS;
-      const size_t item = ((size_t)t0 * a.H + head0 + g + 8 * i) * a.maps + mp;
-      const size_t part = item * parts + (size_t)split * AM_WARPS + warp;
-      float* dst = a.ws_o + part * DV + 2 * tq;
+    }
+  }
+  if (!PROMPT) {
+    // The four warps' states (each over its quarter of every page's keys) meet in shared memory, in warp order: the
+    // block leaves ONE (maximum, sum, O) per row — or, when the positions are not cut, the finished row.
+    constexpr int PW = DV + 2;
+    float* part_s = reinterpret_cast<float*>(v_s);             // [4][16][DV + 2]: fits the value buffers
+    __syncthreads();                                           // everyone is done with the last page
 #pragma unroll
-      for (int j = 0; j < 2 * NV; ++j) *reinterpret_cast<float2*>(dst + 8 * j) = make_float2(o[j][2 * i], o[j][2 * i + 1]);
+    for (int i = 0; i < 2; ++i) {
+      float* dst = part_s + (size_t)(warp * 16 + g + 8 * i) * PW;
+#pragma unroll
+      for (int j = 0; j < 2 * NV; ++j) *reinterpret_cast<float2*>(dst + 8 * j + 2 * tq) = make_float2(o[j][2 * i], o[j][2 * i + 1]);
       if (tq == 0) {
-        a.ws_ml[2 * part] = m_run[i];
-        a.ws_ml[2 * part + 1] = l_run[i];
+        dst[DV] = m_run[i];
+        dst[DV + 1] = l_run[i];
+      }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < group * DV; idx += blockDim.x) {
+      const int r = idx / DV, c = idx - r * DV;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < AM_WARPS; ++w) M = fmaxf(M, part_s[(size_t)(w * 16 + r) * PW + DV]);
+      float acc = 0.f, l = 0.f;
+#pragma unroll
+      for (int w = 0; w < AM_WARPS; ++w) {
+        const float* src = part_s + (size_t)(w * 16 + r) * PW;
+        const float wt = src[DV] == -INFINITY ? 0.f : exp2f(src[DV] - M);
+        acc = fmaf(wt, src[c], acc);
+        l = fmaf(wt, src[DV + 1], l);
+      }
+      const size_t hm = (size_t)(head0 + r) * a.maps + mp;
+      if (a.splits == 1) {
+        const size_t at = (size_t)t0 * a.ldo + hm * DV + c;
+        if (a.out_f32) ((float*)a.out)[at] = acc / l;
+        else ((__nv_bfloat16*)a.out)[at] = __float2bfloat16_rn(acc / l);
+      } else {
+        const size_t part = ((size_t)t0 * a.H * a.maps + hm) * a.splits + split;
+        a.ws_o[part * DV + c] = acc;
+        if (c == 0) {
+          a.ws_ml[2 * part] = M;
+          a.ws_ml[2 * part + 1] = l;
+        }
       }
     }
   }
@@ -346,7 +389,7 @@ LLMI_EXPORT int llmi_attention_maps_mma_supported(int dk, int dv, int group, int
 
 // floats of workspace of a step of single tokens
 LLMI_EXPORT long llmi_attention_maps_mma_workspace(int n_tokens, int n_heads, int maps, int dv, int splits) {
-  return (long)n_tokens * n_heads * maps * splits * AM_WARPS * (dv + 2);
+  return (long)n_tokens * n_heads * maps * splits * (dv + 2);
 }
 
 // prompt != 0: n_blocks = an upper bound of the sum over sequences of ceil(tokens / 128).  prompt == 0: every sequence
@@ -377,11 +420,11 @@ LLMI_EXPORT int llmi_attention_maps_mma(const void* q, long ldq, void* out, long
     if (n_blocks <= 0 || n_heads * maps > 65535) return LLMI_ERR_BAD_SIZE;
     grid = dim3(n_blocks, n_heads * maps);
   } else {
-    if (splits < 1 || pages_per_split < 1 || splits * AM_WARPS > AM_MAX_PARTS || n_kv_heads * maps > 65535 || splits > 65535) return LLMI_ERR_BAD_SIZE;
+    if (splits < 1 || pages_per_split < 1 || splits > AM_MAX_PARTS || n_kv_heads * maps > 65535 || splits > 65535) return LLMI_ERR_BAD_SIZE;
     const long need = llmi_attention_maps_mma_workspace(n_tokens, n_heads, maps, dv, splits);
     if (!workspace || workspace_floats < need) return LLMI_ERR_BAD_SIZE;
     a.ws_o = workspace;
-    a.ws_ml = workspace + (size_t)n_tokens * n_heads * maps * splits * AM_WARPS * dv;
+    a.ws_ml = workspace + (size_t)n_tokens * n_heads * maps * splits * dv;
     grid = dim3(n_seqs, n_kv_heads * maps, splits);
   }
   int rc;
@@ -392,9 +435,9 @@ LLMI_EXPORT int llmi_attention_maps_mma(const void* q, long ldq, void* out, long
     default: return LLMI_ERR_UNSUPPORTED;
   }
 #undef LLMI_CASE
-  if (rc != LLMI_OK || prompt) return rc;
+  if (rc != LLMI_OK || prompt || splits == 1) return rc;
   const long items = (long)n_tokens * n_heads * maps;
   if (items > 0x7fffffffL) return LLMI_ERR_BAD_SIZE;
   return launch_pdl(PDL_SMALL, attention_maps_join_kernel, dim3((unsigned)items), dim3(128), 0, stream, (const float*)a.ws_o,
-                    (const float*)a.ws_ml, out, ldo, out_f32, tok_seq, n_heads * maps, dv, splits * AM_WARPS);
+                    (const float*)a.ws_ml, out, ldo, out_f32, tok_seq, n_heads * maps, dv, splits);
 }
