@@ -37,7 +37,7 @@ class AttentionSizes:
     dim: int
     vdim: int
     scale: float
-    chunk: int               # positions per block of the mask
+    chunk: int               # positions per block of the mask (0: no mask beyond causality)
     diff: float = 0.0        # (two-map attention only)
     rot_base: float = 0.0
     rot_dims: int = 0
@@ -86,10 +86,12 @@ class FusazenConfig:
                 heads, kv_heads = _uint(m, "heads", mw), _uint(m, "kv_heads", mw)
                 if heads % kv_heads:
                     raise ConfigError(f'config: {mw}"heads" is not a multiple of "kv_heads"')
+                # a mixer without "mask" (or with null) sees all earlier positions; one without "rot" is not rotated
+                chunk = _uint(_obj(m, "mask", mw), "size", mw + "mask.", 1 << 30) if m.get("mask") is not None else 0
                 common = dict(heads=heads, kv_heads=kv_heads, dim=_uint(m, "dim", mw), vdim=_uint(m, "vdim", mw),
-                              scale=_number(m, "scale", mw), chunk=_uint(_obj(m, "mask", mw), "size", mw + "mask.", 1 << 30))
+                              scale=_number(m, "scale", mw), chunk=chunk)
                 if kind == "attention":
-                    rot = _obj(m, "rot", mw)
+                    rot = _obj(m, "rot", mw) if m.get("rot") is not None else {"dims": 0, "base": 1.0}
                     rot_dims = _uint(rot, "dims", mw + "rot.", least=0)
                     if rot_dims % 2 or rot_dims > common["dim"]:
                         raise ConfigError(f'config: {mw}rot."dims" must be even and at most "dim"')

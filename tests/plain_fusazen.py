@@ -96,12 +96,18 @@ def masked_attention(q, k, v, scale, mask):
 
 # ----------------------------------------------------------------------------- mixers
 
+def _rotation(m):
+    """(base, rotated entries) of a mixer; one without a rotation has none."""
+    rot = m.get("rot")
+    return (rot["base"], rot["dims"]) if rot else (1.0, 0)
+
+
 def keys_values_diff(h, w, p, m):
     """Rotated keys [T, G, 2, D] and values [T, G, Dv] of a two-map attention layer."""
     T = h.shape[0]
     G, D, Dv = m["kv_heads"], m["dim"], m["vdim"]
     k = (h @ w[p + "k"].T).reshape(T, G * 2, D)
-    k = rotate_halves(k, np.arange(T), m["rot"]["base"], m["rot"]["dims"]).reshape(T, G, 2, D)
+    k = rotate_halves(k, np.arange(T), *_rotation(m)).reshape(T, G, 2, D)
     v = (h @ w[p + "v"].T).reshape(T, G, Dv)
     return k, v
 
@@ -111,10 +117,10 @@ def diff_attention(h, w, p, m, eps, kv):
     T = h.shape[0]
     H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q = (h @ w[p + "q"].T).reshape(T, H * 2, D)
-    q = rotate_halves(q, np.arange(T), m["rot"]["base"], m["rot"]["dims"]).reshape(T, H, 2, D)
+    q = rotate_halves(q, np.arange(T), *_rotation(m)).reshape(T, H, 2, D)
     k, v = kv
     lam = np.exp(np.sum(w[p + "lq1"] * w[p + "lk1"])) - np.exp(np.sum(w[p + "lq2"] * w[p + "lk2"])) + m["diff"]
-    mask = block_mask(T, m["mask"]["size"])
+    mask = block_mask(T, m["mask"]["size"] if m.get("mask") else T)
     out = np.zeros((T, H, Dv))
     for hh in range(H):
         g = hh // (H // G)
@@ -131,7 +137,7 @@ def normed_attention(h, w, p, m, eps):
     q = (rms_unit(h @ w[p + "q"].T, eps) * w[p + "q.norm"]).reshape(T, H, D)
     k = (rms_unit(h @ w[p + "k"].T, eps) * w[p + "k.norm"]).reshape(T, G, D)
     v = (h @ w[p + "v"].T).reshape(T, G, Dv)
-    mask = block_mask(T, m["mask"]["size"])
+    mask = block_mask(T, m["mask"]["size"] if m.get("mask") else T)
     out = np.zeros((T, H, Dv))
     for hh in range(H):
         g = hh // (H // G)

@@ -67,6 +67,15 @@ def test_a_missing_or_ill_typed_key_is_named(damage, word):
     assert word in str(e.value)
 
 
+def test_a_mixer_without_mask_or_rotation_has_none():
+    cfg = copy.deepcopy(M.SHARED)
+    del cfg["layers"][3]["mixer"]["mask"]
+    cfg["layers"][3]["mixer"]["rot"] = None
+    cfg["layers"][5]["mixer"]["rot"] = None
+    _, spec = _spec(cfg)
+    assert spec.layers[3].mixer.params["chunk"] == 0 and spec.layers[3].mixer.params["position"].kind == "none"
+
+
 def test_random_folder_of_the_design(tmp_path):
     import torch
     from llmi_b200 import write_random_model
