@@ -151,20 +151,27 @@ attention_maps_mma_kernel(const MapsArgs a) {
   }
   const int kh = kvh * a.maps + mp;
   const int chunks_v = DV / 8;
-  auto fetch = [&](int pg, int buf) {
-    const int page = a.seq_pages[(size_t)seq * a.pages_stride + pg];
+  // my first 16-byte piece of a key tile and the step from one of my pieces to the next (no division per piece)
+  const int kr0 = threadIdx.x / chunks_k, kc0 = threadIdx.x - kr0 * chunks_k;
+  const int kr_step = blockDim.x / chunks_k, kc_step = blockDim.x - kr_step * chunks_k;
+  auto page_of = [&](int pg) { return pg <= pg_hi ? a.seq_pages[(size_t)seq * a.pages_stride + pg] : -1; };
+  // `page`: the page's index in the cache, read from the table one iteration ahead of its copies
+  auto fetch = [&](int pg, int buf, int page) {
     const __nv_bfloat16* ksrc = a.k_cache + ((size_t)(page < 0 ? 0 : page) * (a.G * a.maps) + kh) * AM_PAGE * dk;
     const __nv_bfloat16* vsrc = a.v_cache + ((size_t)(page < 0 ? 0 : page) * a.G + kvh) * AM_PAGE * DV;
     __nv_bfloat16* kd = k_s + (size_t)buf * AM_PAGE * ldk;
     __nv_bfloat16* vd = v_s + (size_t)buf * AM_PAGE * ldv;
-    for (int idx = threadIdx.x; idx < AM_PAGE * chunks_k; idx += blockDim.x) {
-      const int r = idx / chunks_k, c8 = idx - r * chunks_k;
-      const bool live = page >= 0 && pg * AM_PAGE + r <= newest;
+    const int live_rows = page < 0 ? 0 : newest - pg * AM_PAGE + 1;      // rows of the page that hold a position
+    for (int r = kr0, c8 = kc0; r < AM_PAGE;) {
+      const bool live = r < live_rows;
       cp_async16(kd + r * ldk + 8 * c8, live ? ksrc + (size_t)r * dk + 8 * c8 : a.k_cache, live ? 16 : 0);
+      r += kr_step;
+      c8 += kc_step;
+      if (c8 >= chunks_k) { c8 -= chunks_k; ++r; }
     }
     for (int idx = threadIdx.x; idx < AM_PAGE * chunks_v; idx += blockDim.x) {
       const int r = idx / chunks_v, c8 = idx - r * chunks_v;
-      const bool live = page >= 0 && pg * AM_PAGE + r <= newest;
+      const bool live = r < live_rows;
       cp_async16(vd + r * ldv + 8 * c8, live ? vsrc + (size_t)r * DV + 8 * c8 : a.v_cache, live ? 16 : 0);
     }
     cp_async_commit();
@@ -177,14 +184,16 @@ attention_maps_mma_kernel(const MapsArgs a) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
 
-  if (pg_lo <= pg_hi) fetch(pg_lo, 0);
+  if (pg_lo <= pg_hi) fetch(pg_lo, 0, page_of(pg_lo));
+  int page_next = page_of(pg_lo + 1);
   const int key_off = PROMPT ? 0 : 16 * warp;                    // my keys within a page
   const __nv_bfloat16* a_ptr = q_s + ((PROMPT ? 16 * warp : 0) + (lane & 15)) * ldk + (lane >> 4) * 8;
   for (int pg = pg_lo; pg <= pg_hi; ++pg) {
     const int buf = (pg - pg_lo) & 1;
     cp_async_wait_all();
     __syncthreads();                                             // this page is here; everyone is done with the page before
-    if (pg + 1 <= pg_hi) fetch(pg + 1, buf ^ 1);
+    if (pg + 1 <= pg_hi) fetch(pg + 1, buf ^ 1, page_next);
+    page_next = page_of(pg + 2);
     const int base = pg * AM_PAGE + key_off;
     if (base > w_hi || base + 16 * NT2 - 1 < w_lo) continue;     // nothing here for my rows
     const __nv_bfloat16* kt = k_s + (size_t)buf * AM_PAGE * ldk;
