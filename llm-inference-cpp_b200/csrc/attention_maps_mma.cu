@@ -5,8 +5,9 @@
 // Flash style with mma.sync m16n8k16 (bf16 in, fp32 out): a warp holds 16 query rows; S = Q Kᵀ from shared memory by
 // ldmatrix; the softmax runs on the accumulators with a running maximum and sum per row (fp32, base 2 with the scale
 // folded in); P goes back in as the A operand of O += P V straight from the registers it was computed in.  K and V
-// pages arrive by cp.async into two buffers, the next page while the current one is multiplied; value rows beyond a
-// sequence's newest position arrive as zeros (their weights are zero, and 0 x anything must stay 0).
+// pages arrive by cp.async into two buffers, the next page while the current one is
+// multiplied; value rows beyond a sequence's newest position arrive as zeros (their weights are zero, and 0 x anything
+// must stay 0).
 //
 // Two forms of one kernel:
 //   prompts        a block is 128 consecutive tokens of one sequence and one (head, map): eight warps of 16 rows each,
@@ -29,6 +30,10 @@ namespace llmi {
 
 constexpr int AM_PAGE = 64, AM_WARPS = 4, AM_PAD = 8;      // AM_WARPS: of the form for single tokens
 constexpr int AM_PROMPT_WARPS = 8, AM_PROMPT_ROWS = 16 * AM_PROMPT_WARPS;
+// Page buffers of the form for single tokens.  Measured, a decode step at batch 8 and 4,096 positions: 0.585 ms with two
+// buffers (four blocks fit an SM), 0.600 with three (two pages under way a block, but three blocks an SM); batch 1:
+// 1,899 against 1,915 tokens/s.
+constexpr int AM_TOKEN_BUFFERS = 2;
 
 struct MapsArgs {
   const __nv_bfloat16* q;       // [T, heads, maps, dk]
@@ -60,11 +65,12 @@ attention_maps_mma_kernel(const MapsArgs a) {
   extern __shared__ __align__(16) unsigned char am_smem[];
   pdl_wait();
   pdl_launch_dependents();
-  constexpr int DV = NV * 16, ROWS = PROMPT ? AM_PROMPT_ROWS : 16, NT2 = PROMPT ? 4 : 1;     // NT2: groups of 16 keys a warp takes per page
+  constexpr int DV = NV * 16, ROWS = PROMPT ? AM_PROMPT_ROWS : 16, NT2 = PROMPT ? 4 : 1;
+  constexpr int NBUF = PROMPT ? 2 : AM_TOKEN_BUFFERS;             // page buffers: NBUF - 1 pages are under way while one is multiplied     // NT2: groups of 16 keys a warp takes per page
   const int dk = a.dk, ldk = dk + AM_PAD, ldv = DV + AM_PAD;
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(am_smem);                // [ROWS][ldk]
-  __nv_bfloat16* k_s = q_s + ROWS * ldk;                                          // [2][64][ldk]
-  __nv_bfloat16* v_s = k_s + 2 * AM_PAGE * ldk;                                   // [2][64][ldv]
+  __nv_bfloat16* k_s = q_s + ROWS * ldk;                                          // [NBUF][64][ldk]
+  __nv_bfloat16* v_s = k_s + NBUF * AM_PAGE * ldk;                                // [NBUF][64][ldv]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
   const int group = a.H / a.G;
 
@@ -184,16 +190,21 @@ attention_maps_mma_kernel(const MapsArgs a) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
 
-  if (pg_lo <= pg_hi) fetch(pg_lo, 0, page_of(pg_lo));
-  int page_next = page_of(pg_lo + 1);
+#pragma unroll
+  for (int ahead = 0; ahead < NBUF - 1; ++ahead) {               // (a group per page, also an empty one: the waits count groups)
+    if (pg_lo + ahead <= pg_hi) fetch(pg_lo + ahead, ahead, page_of(pg_lo + ahead));
+    else cp_async_commit();
+  }
+  int page_next = page_of(pg_lo + NBUF - 1);
   const int key_off = PROMPT ? 0 : 16 * warp;                    // my keys within a page
   const __nv_bfloat16* a_ptr = q_s + ((PROMPT ? 16 * warp : 0) + (lane & 15)) * ldk + (lane >> 4) * 8;
   for (int pg = pg_lo; pg <= pg_hi; ++pg) {
-    const int buf = (pg - pg_lo) & 1;
-    cp_async_wait_all();
+    const int buf = (pg - pg_lo) % NBUF;
+    cp_async_wait<NBUF - 2>();
     __syncthreads();                                             // this page is here; everyone is done with the page before
-    if (pg + 1 <= pg_hi) fetch(pg + 1, buf ^ 1, page_next);
-    page_next = page_of(pg + 2);
+    if (pg + NBUF - 1 <= pg_hi) fetch(pg + NBUF - 1, (pg - pg_lo + NBUF - 1) % NBUF, page_next);
+    else cp_async_commit();
+    page_next = page_of(pg + NBUF);
     const int base = pg * AM_PAGE + key_off;
     if (base > w_hi || base + 16 * NT2 - 1 < w_lo) continue;     // nothing here for my rows
     const __nv_bfloat16* kt = k_s + (size_t)buf * AM_PAGE * ldk;
@@ -423,7 +434,8 @@ LLMI_EXPORT int llmi_attention_maps_mma(const void* q, long ldq, void* out, long
   a.scale_log2 = scale * 1.4426950408889634f; a.head_scale = head_scale; a.window = window; a.chunk = chunk;
   a.splits = splits; a.pages_per_split = pages_per_split; a.ws_o = nullptr; a.ws_ml = nullptr;
   const int rows = prompt ? AM_PROMPT_ROWS : 16;
-  const size_t smem = ((size_t)(rows + 2 * AM_PAGE) * (dk + AM_PAD) + (size_t)2 * AM_PAGE * (dv + AM_PAD)) * 2;
+  const int nbuf = prompt ? 2 : AM_TOKEN_BUFFERS;
+  const size_t smem = ((size_t)(rows + nbuf * AM_PAGE) * (dk + AM_PAD) + (size_t)nbuf * AM_PAGE * (dv + AM_PAD)) * 2;
   dim3 grid;
   if (prompt) {
     if (n_blocks <= 0 || n_heads * maps > 65535) return LLMI_ERR_BAD_SIZE;
