@@ -202,6 +202,7 @@ dplr_recurrence_quad_kernel(const float* __restrict__ proj, long ld, const float
     if (s < n) issue(s);
     asm volatile("cp.async.commit_group;" ::: "memory");
   }
+  float2 o_pend = make_float2(0.f, 0.f);                       // my part of the token before's S . r
   for (int i = 0; i < n; ++i) {
     asm volatile("cp.async.wait_group %0;" ::"n"(DPLR_RING - 2) : "memory");
     __syncthreads();                                         // token i's entry is there; token i-1's entry is read out
@@ -225,11 +226,16 @@ dplr_recurrence_quad_kernel(const float* __restrict__ proj, long ld, const float
     }
     dot.x += dot2.x;
     dot.y += dot2.y;
+    // the sums of this token's p . S and of the token BEFORE's S . r ride the same four rounds of shuffles: the latter
+    // are not on the chain from token to token, and a round of their own per token would be
 #pragma unroll
     for (int o = 1; o < 16; o <<= 1) {
       dot.x += __shfl_xor_sync(0xffffffffu, dot.x, o);
       dot.y += __shfl_xor_sync(0xffffffffu, dot.y, o);
+      o_pend.x += __shfl_xor_sync(0xffffffffu, o_pend.x, o);
+      o_pend.y += __shfl_xor_sync(0xffffffffu, o_pend.y, o);
     }
+    if (i > 0 && sub == 0) *reinterpret_cast<float2*>(o_raw + (size_t)(r0 + i - 1) * ldo + (size_t)h * Dv + col0) = o_pend;
     const float2 v = *reinterpret_cast<const float2*>(in + 5 * D + 2 * cg);
     float2 o2 = make_float2(0.f, 0.f), o3 = make_float2(0.f, 0.f);
 #pragma unroll
@@ -255,15 +261,14 @@ dplr_recurrence_quad_kernel(const float* __restrict__ proj, long ld, const float
         }
       }
     }
-    o2.x += o3.x;
-    o2.y += o3.y;
-#pragma unroll
-    for (int o = 1; o < 16; o <<= 1) {
-      o2.x += __shfl_xor_sync(0xffffffffu, o2.x, o);
-      o2.y += __shfl_xor_sync(0xffffffffu, o2.y, o);
-    }
-    if (sub == 0) *reinterpret_cast<float2*>(o_raw + (size_t)(r0 + i) * ldo + (size_t)h * Dv + col0) = o2;
+    o_pend = make_float2(o2.x + o3.x, o2.y + o3.y);           // joined over the lanes in the next token's rounds
   }
+#pragma unroll
+  for (int o = 1; o < 16; o <<= 1) {                           // the last token's
+    o_pend.x += __shfl_xor_sync(0xffffffffu, o_pend.x, o);
+    o_pend.y += __shfl_xor_sync(0xffffffffu, o_pend.y, o);
+  }
+  if (sub == 0) *reinterpret_cast<float2*>(o_raw + (size_t)(r0 + n - 1) * ldo + (size_t)h * Dv + col0) = o_pend;
   asm volatile("cp.async.wait_group 0;" ::: "memory");
   if (write_state && holds) {
 #pragma unroll
